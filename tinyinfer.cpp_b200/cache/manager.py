@@ -28,7 +28,7 @@ from typing import Hashable, Optional, Sequence
 
 import torch
 
-from ..parts.base import FixedStateSpec, PagedKVSpec
+from ..parts.base import CompositeSpec, FixedStateSpec, PagedKVSpec
 from .pages import IdPool, OutOfPages
 
 RELEASED = -1            # block-table entry of a page that a window has passed
@@ -49,6 +49,26 @@ class StateView:
     state: Optional[torch.Tensor]        # [max_requests, *shape]
     slots: Optional[torch.Tensor]        # [requests] int32: the state slot of each request
     writes: bool
+
+
+@dataclass
+class CompositeView:
+    """What a layer that keeps several things sees of its cache slot: a view per name of its
+    ``CompositeSpec`` (names of nested specs are joined by dots)."""
+    parts: dict
+    writes: bool
+
+    def __getitem__(self, name: str):
+        return self.parts[name]
+
+    def sub(self, prefix: str) -> "CompositeView":
+        """The views under ``prefix.`` with the prefix taken off."""
+        cut = prefix + "."
+        return CompositeView({k[len(cut):]: v for k, v in self.parts.items() if k.startswith(cut)}, self.writes)
+
+    def child(self, name: str):
+        """What is kept under ``name``: its view if it is one thing, else the views below it."""
+        return self.parts[name] if name in self.parts else self.sub(name)
 
 
 class _PagedGroup:
@@ -98,7 +118,19 @@ class CacheManager:
         self._state_specs: dict[int, FixedStateSpec] = {}
         self._state_storage: dict[int, torch.Tensor] = {}
         by_spec: dict[PagedKVSpec, int] = {}
+        # a cache slot that keeps several things: every leaf becomes a slot of its own behind the
+        # model's, and the slot's view gathers them under their names
+        self._composite: dict[int, list[tuple[str, int]]] = {}
+        flat_specs = list(cache_specs)
         for slot, spec in enumerate(cache_specs):
+            if isinstance(spec, CompositeSpec):
+                self._composite[slot] = []
+                for name, leaf in spec.flat():
+                    self._composite[slot].append((name, len(flat_specs)))
+                    flat_specs.append(leaf)
+        for slot, spec in enumerate(flat_specs):
+            if isinstance(spec, CompositeSpec):
+                continue
             if isinstance(spec, PagedKVSpec):
                 if spec not in by_spec:
                     by_spec[spec] = len(self.groups)
@@ -278,6 +310,9 @@ class CacheManager:
     def view(self, cache_slot: int, writes: bool, block_tables: Sequence[torch.Tensor],
              state_slots: Optional[torch.Tensor]):
         """The view of ``cache_slot`` for one step, given this step's device tables."""
+        if cache_slot in self._composite:
+            return CompositeView({name: self.view(leaf, writes, block_tables, state_slots)
+                                  for name, leaf in self._composite[cache_slot]}, writes)
         if cache_slot in self._slot_group:
             g, idx = self._slot_group[cache_slot]
             grp = self.groups[g]

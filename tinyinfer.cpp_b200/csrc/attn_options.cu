@@ -383,6 +383,67 @@ attention_options_kernel(const TQ* q, const int* __restrict__ rows, const int* _
     }
 }
 
+// The same with a norm per head: every query head and every key head is divided by its own
+// sqrt(mean(head^2) + eps) and multiplied by a weight of dk elements that all heads share.
+// A warp takes a head; the values are copied by all.
+template <typename TQ, typename TC>
+__global__ void __launch_bounds__(256)
+qk_headnorm_rope_store_kernel(const float* proj, int stride, const float* __restrict__ q_weight,
+                              const float* __restrict__ k_weight, float eps,
+                              const float* __restrict__ inv_freq, int rot,
+                              const int* __restrict__ positions, const int* __restrict__ req_of_tok,
+                              const int* __restrict__ block_table, int bt_stride, TC* __restrict__ pages,
+                              int num_pages, int page_size, int write_kv, int num_heads, int num_kv_heads,
+                              int dk, int dv, TQ* __restrict__ q_out, int* __restrict__ status) {
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nq = num_heads * dk, nk = num_kv_heads * dk, nv = num_kv_heads * dv;
+    const float* row = proj + (size_t)t * stride;
+    const int pos_i = positions[t];
+    const float pos = (float)pos_i;
+    TC* base = nullptr;
+    int slot = 0;
+    if (write_kv) {
+        const int page = block_table[(size_t)req_of_tok[t] * bt_stride + pos_i / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicCAS(status, 0, TI_ERR_BAD_PAGE);
+            return;
+        }
+        slot = pos_i % page_size;
+        base = pages + (size_t)page * num_kv_heads * page_size * (dk + dv);
+    }
+    const int units = num_heads + (write_kv ? num_kv_heads : 0);
+    for (int u = warp; u < units; u += 8) {
+        const bool is_q = u < num_heads;
+        const int h = is_q ? u : u - num_heads;
+        const float* head = row + (is_q ? 0 : nq) + (size_t)h * dk;
+        const float* w = is_q ? q_weight : k_weight;
+        float ss = 0.0f;
+        for (int j = lane; j < dk; j += 32) ss = fmaf(head[j], head[j], ss);
+        const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dk + eps);
+        for (int j = lane; j < dk; j += 32) {
+            float y;
+            if (j < rot) {
+                float s, c;
+                sincosf(pos * inv_freq[j >> 1], &s, &c);
+                const float a = head[j] * inv * (w ? w[j] : 1.0f);
+                const float b = head[j ^ 1] * inv * (w ? w[j ^ 1] : 1.0f);
+                y = (j & 1) ? a * c + b * s : a * c - b * s;
+            } else {
+                y = head[j] * inv * (w ? w[j] : 1.0f);
+            }
+            if (is_q) q_out[(size_t)t * nq + (size_t)h * dk + j] = from_f32<TQ>(y);
+            else base[((size_t)h * page_size + slot) * dk + j] = from_f32<TC>(y);
+        }
+    }
+    if (!write_kv) return;
+    TC* vbase = base + (size_t)num_kv_heads * page_size * dk;
+    const float* vrow = row + nq + nk;
+    for (int e = threadIdx.x; e < nv; e += blockDim.x) {
+        const int j = e % dv, g = e / dv;
+        vbase[((size_t)g * page_size + slot) * dv + j] = from_f32<TC>(vrow[e]);
+    }
+}
+
 }  // namespace
 
 #define TI_DISPATCH_QC(qd, cd, CALL)                                               \
@@ -396,7 +457,7 @@ extern "C" int ti_qk_rownorm_rope_store(const float* proj, int stride, const flo
                                         const int* positions, const int* req_of_tok, const int* block_table,
                                         int bt_stride, void* pages, int cache_dtype, int num_pages,
                                         int page_size, int write_kv, int num_tokens, int num_heads,
-                                        int num_kv_heads, int dk, int dv, void* q_out, int q_dtype,
+                                        int num_kv_heads, int dk, int dv, int per_head, void* q_out, int q_dtype,
                                         int* status, void* stream) {
     if (num_tokens == 0) return 0;
     TI_REQUIRE(rot >= 0 && rot <= dk && rot % 2 == 0, "qk_rownorm_rope_store: rotated width %d must be even "
@@ -404,7 +465,7 @@ extern "C" int ti_qk_rownorm_rope_store(const float* proj, int stride, const flo
     TI_REQUIRE(rot == 0 || inv_freq != nullptr, "qk_rownorm_rope_store: a rotation needs its frequencies");
     cudaStream_t s = (cudaStream_t)stream;
 #define CALL(TQ, TC)                                                                              \
-    qk_rownorm_rope_store_kernel<TQ, TC><<<num_tokens, 256, 0, s>>>(                               \
+    (per_head ? qk_headnorm_rope_store_kernel<TQ, TC> : qk_rownorm_rope_store_kernel<TQ, TC>)<<<num_tokens, 256, 0, s>>>( \
         proj, stride, q_weight, k_weight, eps, inv_freq, rot, positions, req_of_tok, block_table,   \
         bt_stride, (TC*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads, dk, dv,      \
         (TQ*)q_out, status)

@@ -6,7 +6,8 @@
 //     tiles of 64 rows, each inside one expert: {expert, first row, rows}.
 //  2. moe_grouped<GATED>: a block takes one tile of rows and 64 output columns of its expert:
 //     rows of h gathered by token, the expert's gate and up rows, float32 accumulation, and
-//     y = silu(w g) * (w u) in the epilogue (w: the pair's weight), stored in sorted order.
+//     y = silu(w g) * (w u) in the epilogue (w: the pair's weight), stored in sorted order; with
+//     another activation (glu.cuh) the weight scales the output instead: y = w act(g, u).
 //  3. moe_grouped<!GATED>: the same walk over y and the expert's down rows, 128 output columns a
 //     block; the float32 result goes to the pair's own row of a scratch.
 //  4. moe_combine: residual[t] += the rows of t's pairs, in slot order.
@@ -21,6 +22,7 @@
 // tile of products (GATED: 64 gate and 64 up columns, interleaved in runs of 32 so that a warp
 // holds both values of its 32 outputs).
 #include "common.cuh"
+#include "glu.cuh"
 
 namespace {
 
@@ -115,7 +117,7 @@ moe_grouped_kernel(const bf16* a, int lda, const int* __restrict__ sorted_slot,
                    const int* __restrict__ tiles, const int* __restrict__ meta, int top,
                    const bf16* __restrict__ w0, int interleaved, int n, int k,
                    const float* __restrict__ weights, bf16* __restrict__ y_sorted,
-                   float* __restrict__ out_rows) {
+                   float* __restrict__ out_rows, int act, float act_limit, float act_alpha) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ int row_src[BM];                         // the row of `a` behind each row of the tile
     const int tile = blockIdx.y;
@@ -223,7 +225,14 @@ moe_grouped_kernel(const bf16* a, int lda, const int* __restrict__ sorted_slot,
                     if (col >= n) continue;
                     const float g0 = acc[i][j][2 * half] * w, g1 = acc[i][j][2 * half + 1] * w;
                     const float u0 = acc[i][j + 4][2 * half] * w, u1 = acc[i][j + 4][2 * half + 1] * w;
-                    const float y0 = g0 / (1.0f + __expf(-g0)) * u0, y1 = g1 / (1.0f + __expf(-g1)) * u1;
+                    float y0, y1;
+                    if (act == GLU_SILU) {               // the weight scales the expert's input
+                        y0 = g0 / (1.0f + __expf(-g0)) * u0;
+                        y1 = g1 / (1.0f + __expf(-g1)) * u1;
+                    } else {                             // the weight scales the expert's output
+                        y0 = w * glu_activation(act, acc[i][j][2 * half], acc[i][j + 4][2 * half], act_limit, act_alpha);
+                        y1 = w * glu_activation(act, acc[i][j][2 * half + 1], acc[i][j + 4][2 * half + 1], act_limit, act_alpha);
+                    }
                     *reinterpret_cast<__nv_bfloat162*>(dst + col) = __floats2bfloat162_rn(y0, y1);
                 }
             } else {
@@ -374,7 +383,7 @@ extern "C" int ti_moe_grouped(const void* h, int h_stride, const void* w_gate_up
                               const void* w_down, const int* ids, const float* weights, int num_tokens,
                               int top, int experts, int width, int ff, int* sorted_slot, int* tiles,
                               int* meta, void* y_sorted, float* out_rows, float* residual,
-                              int res_stride, void* stream) {
+                              int res_stride, int act, float act_limit, float act_alpha, void* stream) {
     if (num_tokens == 0) return 0;
     TI_REQUIRE(ti_moe_grouped_supported(width, ff, experts),
                "moe_grouped: width %d and expert size %d must be multiples of 32", width, ff);
@@ -395,11 +404,11 @@ extern "C" int ti_moe_grouped(const void* h, int h_stride, const void* w_gate_up
     dim3 g1((ff + BNW / 2 - 1) / (BNW / 2), max_tiles);
     moe_grouped_kernel<true><<<g1, THREADS, SMEM, s>>>(
         (const bf16*)h, h_stride, sorted_slot, tiles, meta, top, (const bf16*)w_gate_up, interleaved, ff, width,
-        weights, (bf16*)y_sorted, nullptr);
+        weights, (bf16*)y_sorted, nullptr, act, act_limit, act_alpha);
     dim3 g2((width + BNW - 1) / BNW, max_tiles);
     moe_grouped_kernel<false><<<g2, THREADS, SMEM, s>>>(
         (const bf16*)y_sorted, ff, sorted_slot, tiles, meta, top, (const bf16*)w_down, 0, width, ff,
-        nullptr, nullptr, out_rows);
+        nullptr, nullptr, out_rows, 0, 0.0f, 0.0f);
     const size_t total = (size_t)num_tokens * width;
     moe_combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(out_rows, top, width, num_tokens,
                                                                        residual, res_stride);

@@ -2,12 +2,14 @@
 // every operand type.
 //
 //  * router_topk: per token the `top` experts of largest logit (ties: the lower index) with the
-//    sigmoid of their logits as weights; one more column of the same product, if there is one,
+//    sigmoid of their logits as weights (or, `softmax`, their share of the softmax over all
+//    experts, not renormalised); one more column of the same product, if there is one,
 //    becomes the sigmoid gate of a shared expert.
 //  * moe_gate_up_simple: y[t][s] = silu(w g) * (w u) with g = Wgate_e h_t, u = Wup_e h_t, e and w
 //    the expert and weight of the token's slot s (an expert's gate and up rows are stacked in one
 //    matrix, interleaved in strips of 8 or one after the other).  The weight stands for a scaling of the
-//    expert's input: (Wgate (w h), Wup (w h)) = (w g, w u).
+//    expert's input: (Wgate (w h), Wup (w h)) = (w g, w u).  With another activation (glu.cuh) the
+//    weight scales the expert's output: y = w act(g, u).
 //  * moe_down_simple: out[t] += sum over the slots, in order, of Wdown_e y[t][s].
 //  Both take a shared expert along when one is given: its gate/up products as one more pair per
 //  token with weight 1, its down product added to the token's sum times the token's gate.
@@ -17,6 +19,7 @@
 // accumulation, k ascending inside a lane's share and a fixed butterfly across lanes, so a
 // row's bits do not depend on what else is in the batch.
 #include "common.cuh"
+#include "glu.cuh"
 
 namespace {
 
@@ -65,7 +68,7 @@ __device__ __forceinline__ void lane_dots(const TA* __restrict__ x, const TW* __
 __global__ void __launch_bounds__(WARPS * 32)
 router_topk_kernel(const float* logits, int stride, int num_tokens, int experts, int top,
                    int shared_col, int* __restrict__ ids, float* __restrict__ weights,
-                   float* __restrict__ shared_gate) {
+                   float* __restrict__ shared_gate, int softmax) {
     __shared__ int chosen[WARPS][MAX_TOP];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * WARPS + warp;
@@ -81,6 +84,15 @@ router_topk_kernel(const float* logits, int stride, int num_tokens, int experts,
         const int e = lane + 32 * i;
         mine[i] = held && e < experts ? z[e] : 0.0f;
         gone[i] = !(held && e < experts);
+    }
+    float z_max = 0.0f, z_sum = 1.0f;                 // softmax over all experts: exp(z - max) / sum
+    if (softmax) {
+        float m = -INFINITY;
+        for (int e = lane; e < experts; e += 32) m = fmaxf(m, z[e]);
+        z_max = warp_max(m);
+        float acc = 0.0f;
+        for (int e = lane; e < experts; e += 32) acc += expf(z[e] - z_max);
+        z_sum = warp_sum(acc);
     }
     for (int s = 0; s < top; ++s) {
         float best = -INFINITY;
@@ -113,7 +125,7 @@ router_topk_kernel(const float* logits, int stride, int num_tokens, int experts,
         if (lane == 0) {
             chosen[warp][s] = best_e;
             ids[(size_t)t * top + s] = best_e;
-            weights[(size_t)t * top + s] = sigmoidf_(best);
+            weights[(size_t)t * top + s] = softmax ? expf(best - z_max) / z_sum : sigmoidf_(best);
         }
         __syncwarp();
     }
@@ -127,7 +139,8 @@ moe_gate_up_simple_kernel(const TA* __restrict__ h, int h_stride, const TW* __re
                           int interleaved, const int* __restrict__ ids,
                           const float* __restrict__ weights, int top, int width, int ff,
                           TA* __restrict__ y, int n_pairs, const TW* __restrict__ shared_gate_up,
-                          int shared_interleaved, int shared_ff, TA* __restrict__ y_shared) {
+                          int shared_interleaved, int shared_ff, TA* __restrict__ y_shared,
+                          int act, float act_limit, float act_alpha) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int ts = blockIdx.x;                              // token * top + slot; behind the pairs: a token's shared expert
     const int f = blockIdx.y * WARPS + warp;
@@ -150,9 +163,14 @@ moe_gate_up_simple_kernel(const TA* __restrict__ h, int h_stride, const TW* __re
     const TW* wu = w_gate_up + ((size_t)e * 2 * ff + up_row) * width;
     float g, u;
     lane_dots(x, wg, wu, width, lane, g, u);
-    g = warp_sum(g) * w;
-    u = warp_sum(u) * w;
-    if (lane == 0) y[(size_t)ts * ff + f] = from_f32<TA>(g * sigmoidf_(g) * u);
+    g = warp_sum(g);
+    u = warp_sum(u);
+    if (lane == 0) {
+        // silu: the weight scales the expert's input; other activations: its output
+        const float out = act == GLU_SILU ? (g * w) * sigmoidf_(g * w) * (u * w)
+                                          : w * glu_activation(act, g, u, act_limit, act_alpha);
+        y[(size_t)ts * ff + f] = from_f32<TA>(out);
+    }
 }
 
 template <typename TA, typename TW>
@@ -206,12 +224,12 @@ __global__ void scale_rows_kernel(T* __restrict__ y, int stride, const float* __
 
 extern "C" int ti_router_topk(const float* logits, int stride, int num_tokens, int experts, int top,
                               int shared_col, int* ids, float* weights, float* shared_gate,
-                              void* stream) {
+                              int softmax, void* stream) {
     if (num_tokens == 0) return 0;
     TI_REQUIRE(top >= 1 && top <= MAX_TOP && top <= experts,
                "router_topk: %d of %d experts (at most %d are chosen)", top, experts, MAX_TOP);
     router_topk_kernel<<<(num_tokens + WARPS - 1) / WARPS, WARPS * 32, 0, (cudaStream_t)stream>>>(
-        logits, stride, num_tokens, experts, top, shared_col, ids, weights, shared_gate);
+        logits, stride, num_tokens, experts, top, shared_col, ids, weights, shared_gate, softmax);
     return ti_check_launch("router_topk");
 }
 
@@ -219,7 +237,8 @@ extern "C" int ti_moe_gate_up_simple(const void* h, int act_dtype, int h_stride,
                                      int interleaved, int w_dtype, const int* ids,
                                      const float* weights, int num_tokens, int top, int width, int ff,
                                      void* y, const void* shared_gate_up, int shared_interleaved,
-                                     int shared_ff, void* y_shared, void* stream) {
+                                     int shared_ff, void* y_shared, int act, float act_limit,
+                                     float act_alpha, void* stream) {
     if (num_tokens == 0) return 0;
     // with a shared expert (same weight dtype): one more "pair" per token behind the routed ones
     const bool shared = shared_gate_up != nullptr;
@@ -229,7 +248,8 @@ extern "C" int ti_moe_gate_up_simple(const void* h, int act_dtype, int h_stride,
 #define CALL(TA, TW)                                                                         \
     moe_gate_up_simple_kernel<TA, TW><<<grid, WARPS * 32, 0, s>>>(                            \
         (const TA*)h, h_stride, (const TW*)w_gate_up, interleaved, ids, weights, top, width, ff, (TA*)y, \
-        num_tokens * top, (const TW*)shared_gate_up, shared_interleaved, shared_ff, (TA*)y_shared)
+        num_tokens * top, (const TW*)shared_gate_up, shared_interleaved, shared_ff, (TA*)y_shared, \
+        act, act_limit, act_alpha)
     TI_DISPATCH_AW(act_dtype, w_dtype, CALL)
 #undef CALL
     return ti_check_launch("moe_gate_up_simple");

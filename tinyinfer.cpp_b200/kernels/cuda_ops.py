@@ -13,6 +13,7 @@ embed(table, token_ids, out)                 out[t] = float32(table[token_ids[t]
 rmsnorm(x, weight, eps, out, rows=None)      out[r] = norm(x[rows[r]] or x[r]), rounded to out.dtype
 linear(a, w, out, accumulate=False)          out (+)= a @ w.T in float32
 linear_xielu(h, w, ap, aq, out)              out = xielu(h @ w.T), one launch for few rows
+glu_ffn(h, w_gate_up, w_down, residual, ...) residual += act(gate, up) @ w_down.T with a gated activation
 gate_up_swiglu(h, w, out)                    out = silu(h @ gate.T) * (h @ up.T)
 qk_norm_rope_store(qkv, ..., rotation, ...)  q/k head norm, rotation, k/v into pages, q out
 qkv_rope_store(h, w, ..., rotation, ...)     the QKV product followed by qk_norm_rope_store, in one
@@ -38,6 +39,7 @@ import torch
 
 from .build import load_library
 from .mixer_ops import MixerOps
+from .state_ops import StateOps
 
 _CODE = {torch.float32: 0, torch.bfloat16: 1}
 _vp = ctypes.c_void_p
@@ -111,7 +113,7 @@ def choose_prompt_attention(n_tiles: int, num_heads: int, num_sms: int, *, reach
     return two, runs
 
 
-class CudaOps(MixerOps):
+class CudaOps(MixerOps, StateOps):
     name = "cuda"
 
     def __init__(self, device):
@@ -210,9 +212,9 @@ class CudaOps(MixerOps):
                                              _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp]
         c.ti_attention_bias_simple.argtypes = [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
                                                _i, _i, _i, _i, _f, _vp, _i, _vp, _i, _vp, _vp, _vp]
-        c.ti_router_topk.argtypes = [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]
+        c.ti_router_topk.argtypes = [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp]
         c.ti_moe_gate_up_simple.argtypes = [_vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _i,
-                                            _vp, _vp]
+                                            _vp, _i, _f, _f, _vp]
         c.ti_moe_down_simple.argtypes = [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _i, _vp]
         c.ti_scale_rows.argtypes = [_vp, _i, _i, _vp, _i, _i, _vp]
 
@@ -286,7 +288,7 @@ class CudaOps(MixerOps):
                                               _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp]
             b.ti_moe_grouped_supported.argtypes = [_i, _i, _i]
             b.ti_moe_grouped.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp,
-                                         _vp, _vp, _i, _vp]
+                                         _vp, _vp, _i, _i, _f, _f, _vp]
             b.ti_moe_sort_padded.argtypes = [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]
             b.ti_moe_gather_scaled.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp]
             b.ti_moe_combine_rows.argtypes = [_vp, _vp, _i, _i, _i, _vp, _i, _vp]
@@ -555,6 +557,21 @@ class CudaOps(MixerOps):
         z = torch.empty((m, n), dtype=torch.float32, device=h.device)
         self.linear(h, w, z)
         self.xielu_rows(z, ap, aq, out)
+
+    def glu_ffn(self, h, w_gate_up, w_down, residual, kind, limit, alpha, row_scale=None):
+        """residual += act(h Wgate^T, h Wup^T) Wdown^T with ``w_gate_up`` from pack_gate_up and the
+        gated activation ``kind`` of ``glu_rows`` ("clamped": ``g = min(g, limit)``, ``u = clamp(u,
+        -limit, limit)``, ``g sigmoid(alpha g) (u + 1)``); ``row_scale`` (float32, one per row)
+        multiplies a row's activations."""
+        m = h.shape[0]
+        inter = w_down.shape[1]
+        gu = torch.empty((m, 2 * inter), dtype=torch.float32, device=h.device)
+        self.linear(h, w_gate_up, gu)
+        y = torch.empty((m, inter), dtype=h.dtype, device=h.device)
+        self.glu_rows(gu, bool(getattr(w_gate_up, "_ti_interleaved", False)), kind, limit, alpha, y)
+        if row_scale is not None:
+            self.scale_rows(y, row_scale)
+        self.linear(y, w_down, residual, accumulate=True)
 
     def swiglu_ffn(self, h, w_gate_up, w_down, residual, may_defer=False):
         """residual += (silu(h Wgate^T) * (h Wup^T)) Wdown^T, with ``w_gate_up`` from pack_gate_up.
@@ -1022,10 +1039,11 @@ class CudaOps(MixerOps):
             gate_up = torch.cat([gate, up], dim=1).contiguous()
         return {"gate_up": gate_up, "down": down.contiguous(), "interleaved": interleaved}
 
-    def router_topk(self, logits, experts, top, ids, weights, shared_gate=None):
+    def router_topk(self, logits, experts, top, ids, weights, shared_gate=None, softmax=False):
         """Per row the ``top`` largest of the first ``experts`` logits (ties: the lower index):
         ``ids`` int32 and ``weights = sigmoid(logit)`` float32, both ``[rows, top]``; with
-        ``shared_gate`` also ``sigmoid(logits[:, experts])`` per row."""
+        ``shared_gate`` also ``sigmoid(logits[:, experts])`` per row.  ``softmax``: the weights are
+        the chosen experts' shares of the softmax over all ``experts`` logits, not renormalised."""
         t = logits.shape[0]
         _need(logits.dtype == torch.float32 and logits.stride(1) == 1
               and logits.shape[1] >= experts + (shared_gate is not None), "router_topk: float32 logits")
@@ -1034,15 +1052,18 @@ class CudaOps(MixerOps):
               "router_topk: ids int32 and weights float32, [rows, top]")
         self._ok(self.core.ti_router_topk(logits.data_ptr(), logits.stride(0), t, experts, top,
                                           experts if shared_gate is not None else -1, ids.data_ptr(),
-                                          weights.data_ptr(), _ptr(shared_gate), self._stream()))
+                                          weights.data_ptr(), _ptr(shared_gate), int(bool(softmax)),
+                                          self._stream()))
 
-    def routed_experts(self, h, w, ids, weights, residual, shared=None):
+    def routed_experts(self, h, w, ids, weights, residual, shared=None, act=None):
         """residual[t] += sum over slots s of Wdown_e (silu(w g) * (w u)), g = Wgate_e h[t],
         u = Wup_e h[t], e = ids[t, s], w = weights[t, s].  ``shared`` (may be None):
         ``(w_gate_up from pack_gate_up, w_down, gate)`` of an expert that every token uses, its
         output times ``gate[t]``: residual[t] += gate[t] * Wdown (silu(g) * u).  Few tokens run
-        it inside the experts' two launches."""
-        self._routed(h, w, ids, weights, residual, shared)
+        it inside the experts' two launches.  ``act`` (may be None: silu) names another gated
+        activation, ``(kind, limit, alpha)`` as ``glu_rows`` takes them; the pair's weight then
+        scales the expert's output, residual[t] += w Wdown_e act(g, u), and there is no ``shared``."""
+        self._routed(h, w, ids, weights, residual, shared, act)
 
     def _shared_expert(self, h, shared, residual):
         w_gate_up, w_down, gate = shared
@@ -1051,7 +1072,10 @@ class CudaOps(MixerOps):
         self.scale_rows(y, gate)
         self.linear(y, w_down, residual, accumulate=True)
 
-    def _routed(self, h, w, ids, weights, residual, shared):
+    def _routed(self, h, w, ids, weights, residual, shared, act=None):
+        from .state_ops import GLU_KINDS
+        act_kind, act_limit, act_alpha = (0, 0.0, 0.0) if act is None else (GLU_KINDS[act[0]], float(act[1]), float(act[2]))
+        _need(act_kind == 0 or shared is None, "routed_experts: a shared expert rides only with the silu activation")
         t, width = h.shape
         top = ids.shape[1]
         experts, ff = w["down"].shape[0], w["down"].shape[2]
@@ -1067,7 +1091,7 @@ class CudaOps(MixerOps):
                 and self.gated.ti_moe_grouped_supported(width, ff, experts)):
             pairs = t * top
             if (self.tcgen05_experts_from is not None and pairs >= self.tcgen05_experts_from and interleaved
-                    and ff % 16 == 0 and width % 8 == 0):
+                    and ff % 16 == 0 and width % 8 == 0 and act_kind == 0):
                 # every expert's pairs in whole tiles of 128 rows, the rows of h times their weights
                 # gathered in that order, two grouped tcgen05 products (the first with SwiGLU in its
                 # epilogue), and the pairs' rows added per token
@@ -1105,7 +1129,8 @@ class CudaOps(MixerOps):
                 h.data_ptr(), h.stride(0), gate_up.data_ptr(), interleaved, w["down"].data_ptr(),
                 ids.data_ptr(), weights.data_ptr(), t, top, experts, width, ff, ints.data_ptr(),
                 ints[pairs:].data_ptr(), ints[ints.shape[0] - 1:].data_ptr(), y_sorted.data_ptr(),
-                out_rows.data_ptr(), residual.data_ptr(), residual.stride(0), self._stream()), self.gated)
+                out_rows.data_ptr(), residual.data_ptr(), residual.stride(0), act_kind, act_limit, act_alpha,
+                self._stream()), self.gated)
             self.launches += 3
             if shared is not None:
                 self._shared_expert(h, shared, residual)
@@ -1129,7 +1154,7 @@ class CudaOps(MixerOps):
         self._ok(self.core.ti_moe_gate_up_simple(
             h.data_ptr(), _code(h, "routed_experts"), h.stride(0), gate_up.data_ptr(), interleaved,
             _code(gate_up, "routed_experts"), ids.data_ptr(), weights.data_ptr(), t, top, width, ff,
-            y.data_ptr(), _ptr(sgu), s_inter, s_ff, _ptr(y_sh), self._stream()))
+            y.data_ptr(), _ptr(sgu), s_inter, s_ff, _ptr(y_sh), act_kind, act_limit, act_alpha, self._stream()))
         self._ok(self.core.ti_moe_down_simple(
             y.data_ptr(), _code(y, "routed_experts"), w["down"].data_ptr(), _code(w["down"], "routed_experts"),
             ids.data_ptr(), t, top, width, ff, residual.data_ptr(), residual.stride(0), _ptr(y_sh), _ptr(sdown),
@@ -1185,7 +1210,7 @@ def _flush_first(fn):
     return wrapper
 
 
-for _name, _fn in list(vars(MixerOps).items()) + list(vars(CudaOps).items()):
+for _name, _fn in list(vars(MixerOps).items()) + list(vars(StateOps).items()) + list(vars(CudaOps).items()):
     if (isinstance(_fn, type(_flush_first)) and not _name.startswith("_")
             and _name not in ("flush", "linear", "rmsnorm", "swiglu_ffn")):
         setattr(CudaOps, _name, _flush_first(_fn))

@@ -77,7 +77,7 @@ class MixerOps:
             b = load_library("mixers")
             b.ti_last_error.restype = ctypes.c_char_p
             b.ti_qk_rownorm_rope_store.argtypes = [_vp, _i, _vp, _vp, _f, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i,
-                                                   _i, _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp]
+                                                   _i, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp]
             b.ti_latent_prepare.argtypes = [_vp, _i, _vp, _f, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
                                             _i, _i, _vp, _vp, _i, _vp, _vp]
             b.ti_head_project.argtypes = [_vp, _i, _i, _i, _vp, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _vp]
@@ -102,12 +102,14 @@ class MixerOps:
 
     # ---- preparing heads ---------------------------------------------------------------------
     def qk_rownorm_rope_store(self, proj, q_weight, k_weight, eps, rotation, step, cache, q_out,
-                              num_heads, num_kv_heads, dk, dv):
+                              num_heads, num_kv_heads, dk, dv, per_head=False):
         """From the float32 product ``proj`` (columns: queries, keys, values, then anything else):
         RMS norm over the whole query row and over the whole key row (weights of that length, or
         None), rotation of the first ``rotation.rotary_dim`` elements of every head in neighbouring
         pairs (kind ``interleaved``) or none, keys and values into the token's page (if the cache
-        slot is written), queries into ``q_out``."""
+        slot is written), queries into ``q_out``.  ``per_head``: every query head and every key
+        head is normed by itself (RMS over ``dk``) with a weight of ``dk`` elements that all heads
+        share."""
         t = proj.shape[0]
         pages, bt = cache.pages, cache.block_table
         nq, nk, nv = num_heads * dk, num_kv_heads * dk, num_kv_heads * dv
@@ -117,7 +119,7 @@ class MixerOps:
         self._must(proj.dtype == torch.float32 and proj.stride(1) == 1
                    and proj.shape[1] >= nq + (nk + nv if cache.writes else 0),
                    "qk_rownorm_rope_store: the product must be float32 and hold all heads")
-        for w, n in ((q_weight, nq), (k_weight, nk)):
+        for w, n in ((q_weight, dk if per_head else nq), (k_weight, dk if per_head else nk)):
             self._must(w is None or (w.dtype == torch.float32 and w.is_contiguous() and w.shape[0] == n),
                        "qk_rownorm_rope_store: a norm weight must be float32, one value per column")
         self._must(rot == 0 or (rotation.inv_freq is not None and rotation.inv_freq.dtype == torch.float32
@@ -131,8 +133,8 @@ class MixerOps:
             proj.data_ptr(), proj.stride(0), _ptr(q_weight), _ptr(k_weight), float(eps),
             _ptr(rotation.inv_freq) if rot else None, rot, step.positions.data_ptr(), step.req_of_tok.data_ptr(),
             bt.data_ptr(), bt.stride(0), pages.data_ptr(), _CODE[pages.dtype], pages.shape[0], cache.page_size,
-            int(bool(cache.writes)), t, num_heads, num_kv_heads, dk, dv, q_out.data_ptr(), _CODE[q_out.dtype],
-            self.status.data_ptr(), self._stream()))
+            int(bool(cache.writes)), t, num_heads, num_kv_heads, dk, dv, int(bool(per_head)), q_out.data_ptr(),
+            _CODE[q_out.dtype], self.status.data_ptr(), self._stream()))
 
     def latent_prepare(self, proj, latent_weight, eps, rotation, step, cache, q_plain, q_full,
                        num_heads, dk, dr, rank):

@@ -39,6 +39,7 @@ NORM_ZERO = "norm0"      # random mode: N(0, 0.02), stored in float32 (a factor 
 class WeightSpec:
     shape: tuple[int, ...]           # an entry may be None: the stored tensor decides that size
     init: str = MATRIX
+    optional: bool = False           # a folder may lack the tensor: the part then gets None for it
 
 
 @dataclass(frozen=True)
@@ -62,6 +63,25 @@ class FixedStateSpec:
     """Per-request state of fixed size, zero when a request starts."""
     shape: tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class CompositeSpec:
+    """Several things kept per request by one layer, each under a name: for instance the pages of
+    an attention beside the fixed-size state of a recurrent mixer that reads the same input, or a
+    mixer's cache beside what the block around it keeps.  The layer's view of its cache slot is
+    then a ``CompositeView`` with one view per name."""
+    items: tuple[tuple[str, "PagedKVSpec | FixedStateSpec | CompositeSpec"], ...]
+
+    def flat(self, prefix: str = "") -> list:
+        """``(dotted name, leaf spec)`` of every leaf, in order."""
+        out = []
+        for name, spec in self.items:
+            if isinstance(spec, CompositeSpec):
+                out += spec.flat(prefix + name + ".")
+            elif spec is not None:
+                out.append((prefix + name, spec))
+        return out
 
 
 class Part:

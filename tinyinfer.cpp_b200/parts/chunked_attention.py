@@ -13,7 +13,9 @@ For token ``i`` and query head ``a`` (kv head ``a // (heads / kv_heads)``):
 * head ``a``'s output times ``sigmoid((Wg h)[a])``, then ``residual += Wo (.)``.
 
 ``Wq, Wk, Wv, Wg`` run as one product.  Every option can be left out (``chunk``, ``window``,
-``softcap`` None; ``head_temperature``, ``head_gate`` False), so other designs can use the part.
+``softcap`` None; ``head_temperature``, ``head_gate`` False), and ``norm_per_head`` norms every
+query and key head by itself with one weight of ``head_dim`` elements, so other designs can use the
+part: with everything off it is plain causal grouped-query attention with a query/key norm.
 """
 from __future__ import annotations
 
@@ -31,7 +33,7 @@ class ChunkedAttention(Part):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int,
                  scale: float, qk_norm_eps: float, position: PartSpec, chunk: Optional[int] = None,
                  window: Optional[int] = None, softcap: Optional[float] = None,
-                 head_temperature: bool = True, head_gate: bool = True):
+                 head_temperature: bool = True, head_gate: bool = True, norm_per_head: bool = False):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads cannot share {num_kv_heads} kv heads evenly")
         for name, v in (("chunk", chunk), ("window", window)):
@@ -45,6 +47,9 @@ class ChunkedAttention(Part):
         self.window = None if window is None else int(window)
         self.softcap = None if softcap is None else float(softcap)
         self.head_temperature, self.head_gate = bool(head_temperature), bool(head_gate)
+        # the norm of queries and keys: over the whole row with a weight per column, or over each
+        # head by itself with a weight of head_dim elements that all heads share
+        self.norm_per_head = bool(norm_per_head)
         self.position = build_part("position", position)
         self.nq, self.nk = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
         self.nv, self.no = self.num_kv_heads * self.v_head_dim, self.num_heads * self.v_head_dim
@@ -54,7 +59,8 @@ class ChunkedAttention(Part):
         h = self.hidden_size
         specs = {"q": WeightSpec((self.nq, h), MATRIX), "k": WeightSpec((self.nk, h), MATRIX),
                  "v": WeightSpec((self.nv, h), MATRIX), "o": WeightSpec((h, self.no), MATRIX),
-                 "q.norm": WeightSpec((self.nq,), NORM_WEIGHT), "k.norm": WeightSpec((self.nk,), NORM_WEIGHT)}
+                 "q.norm": WeightSpec((self.head_dim if self.norm_per_head else self.nq,), NORM_WEIGHT),
+                 "k.norm": WeightSpec((self.head_dim if self.norm_per_head else self.nk,), NORM_WEIGHT)}
         if self.head_temperature:
             specs["temp"] = WeightSpec((self.num_heads,), NORM_WEIGHT)
         if self.head_gate:
@@ -84,7 +90,7 @@ class ChunkedAttention(Part):
         q = torch.empty((t, self.nq), dtype=h.dtype, device=h.device)
         ops.qk_rownorm_rope_store(proj, self.q_norm, self.k_norm, self.eps, self.position.rotation(h.device),
                                   step, cache, q, self.num_heads, self.num_kv_heads, self.head_dim,
-                                  self.v_head_dim)
+                                  self.v_head_dim, per_head=self.norm_per_head)
         gate = proj[:, self.nq + self.nk + self.nv:] if self.head_gate else None
         out = torch.empty((t, self.no), dtype=h.dtype, device=h.device)
         ops.attention_options(q, step, cache, out, self.num_heads, self.num_kv_heads, self.head_dim,

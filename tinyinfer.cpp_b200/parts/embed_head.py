@@ -16,15 +16,16 @@ from .base import MATRIX, NORM_WEIGHT, NORM_ZERO, Part, WeightSpec, as_float32, 
 class Embedding(Part):
     category = "embedding"
 
-    def __init__(self, vocab_size: int, hidden_size: int):
+    def __init__(self, vocab_size: int, hidden_size: int, tensor: str = "weight"):
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.tensor = str(tensor)            # the table's name behind the part's prefix
         self.table = None
 
     def weight_specs(self):
-        return {"weight": WeightSpec((self.vocab_size, self.hidden_size), MATRIX)}
+        return {self.tensor: WeightSpec((self.vocab_size, self.hidden_size), MATRIX)}
 
     def load_weights(self, tensors, ops):
-        self.table = ops.pack_linear(tensors["weight"])
+        self.table = ops.pack_linear(tensors[self.tensor])
 
     def shared_weights(self):
         return {"weight": self.table}

@@ -5,6 +5,8 @@ gate and up as one product over stacked rows, src/inference.cu:59-65).  How the
 gate and up rows are stacked is the kernel set's choice (``ops.pack_gate_up``).
 
 ``xielu_mlp``: an ungated feed-forward with the xIELU activation (below).
+
+``glu_mlp``: a gated feed-forward with a named activation and its constants (below).
 """
 from __future__ import annotations
 
@@ -77,3 +79,36 @@ class XieluMlp(Part):
 
 
 register_part("ffn", "xielu_mlp", XieluMlp)
+
+
+class GatedMlp(Part):
+    """``residual += Wdown act(Wgate h, Wup h)`` with the gated activation ``activation``:
+
+    ``silu``     ``silu(g) u``
+    ``clamped``  ``g = min(g, limit)``, ``u = clamp(u, -limit, limit)``, ``g sigmoid(alpha g) (u + 1)``
+
+    The tensors are ``gate``, ``up`` and ``down``."""
+    category = "ffn"
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "clamped", limit: float = 0.0,
+                 alpha: float = 1.702):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.activation, self.limit, self.alpha = str(activation), float(limit), float(alpha)
+        self.w_gate_up = self.w_down = None
+
+    def weight_specs(self):
+        h, i = self.hidden_size, self.intermediate_size
+        return {"gate": WeightSpec((i, h), MATRIX), "up": WeightSpec((i, h), MATRIX), "down": WeightSpec((h, i), MATRIX)}
+
+    def load_weights(self, tensors, ops):
+        g, u = tensors["gate"], tensors["up"]
+        if g.dtype != u.dtype:
+            g, u = g.to(torch.float32), u.to(torch.float32)
+        self.w_gate_up = ops.pack_gate_up(g, u)
+        self.w_down = ops.pack_linear(tensors["down"])
+
+    def forward(self, ops, h, residual, step):
+        ops.glu_ffn(h, self.w_gate_up, self.w_down, residual, self.activation, self.limit, self.alpha)
+
+
+register_part("ffn", "glu_mlp", GatedMlp)

@@ -35,6 +35,8 @@ class CausalLM:
                 "ffn_norm": None if lp.ffn_norm is None else build_part("norm", lp.ffn_norm),
             }
             self.blocks.append(build_part("block", lp.block, **parts))
+            if "block" in lp.names:            # an arrangement with tensors of its own
+                self._named.append((lp.names["block"], self.blocks[-1]))
             for role, part in parts.items():
                 if part is not None:
                     self._named.append((lp.names[role], part))
@@ -58,11 +60,14 @@ class CausalLM:
             return {self.plan.names["head"] + "weight": self.plan.names["embedding"] + local}
         return {}
 
-    def load_weights(self, fetch: Callable[[str], torch.Tensor], ops) -> None:
-        """``fetch(name)`` returns the checkpoint tensor on the device, dtype as stored."""
+    def load_weights(self, fetch: Callable[[str], torch.Tensor], ops, present=None) -> None:
+        """``fetch(name)`` returns the checkpoint tensor on the device, dtype as stored;
+        ``present(name)`` (if given) says whether the source holds a tensor: an optional one
+        that it lacks reaches its part as None."""
         for prefix, part in self._named:
             names = part.weight_specs()
-            part.load_weights({local: fetch(prefix + local) for local in names}, ops)
+            part.load_weights({local: None if (spec.optional and present is not None and not present(prefix + local))
+                               else fetch(prefix + local) for local, spec in names.items()}, ops)
         if getattr(self.head, "tied", False):
             self.head.tie(self.embedding)
 
@@ -79,7 +84,9 @@ class CausalLM:
         """What each cache slot of the schedule holds (from the mixer that writes it)."""
         specs: list = [None] * self.plan.num_cache_slots
         for entry in self.plan.schedule:
-            spec = self.blocks[entry.layer].mixer.cache_spec()
+            block = self.blocks[entry.layer]
+            # a block that keeps something itself answers for its mixer too
+            spec = block.cache_spec() if hasattr(block, "cache_spec") else block.mixer.cache_spec()
             if entry.writes_cache:
                 specs[entry.cache_slot] = spec
             elif specs[entry.cache_slot] != spec:

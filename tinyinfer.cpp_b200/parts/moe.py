@@ -10,6 +10,12 @@ by a sigmoid router, plus an optional shared expert behind a sigmoid gate of its
   multiplied by ``sigmoid(wsg . h)``, one number per token; ``wsg`` rides as one more row of the
   router's product.
 * ``residual +=`` the sum.
+
+Options for other designs: ``router = "softmax"`` takes the chosen experts' shares of the softmax
+over all experts as weights (not renormalised); ``activation = (kind, limit, alpha)`` names another
+gated activation for the experts (``parts/mlp.py``), and the weight then scales the expert's
+output, ``w Wdown_e act(Wgate_e h, Wup_e h)``; ``shared_gated = False`` leaves the shared expert's
+sigmoid gate out (no ``shared.sg``); ``shared_activation`` is the shared expert's own activation.
 """
 from __future__ import annotations
 
@@ -24,12 +30,20 @@ class RoutedExperts(Part):
     category = "ffn"
 
     def __init__(self, hidden_size: int, experts: int, top: int, expert_size: int,
-                 shared_size: Optional[int] = None):
+                 shared_size: Optional[int] = None, router: str = "sigmoid", activation=None,
+                 shared_gated: bool = True, shared_activation=None):
         if not 1 <= top <= experts:
             raise ValueError(f"{top} of {experts} experts cannot be chosen")
         self.hidden_size, self.experts, self.top = int(hidden_size), int(experts), int(top)
         self.expert_size = int(expert_size)
         self.shared_size = None if shared_size is None else int(shared_size)
+        if router not in ("sigmoid", "softmax"):
+            raise ValueError(f"router kind {router!r}; known: sigmoid, softmax")
+        self.router = router
+        self.activation = None if activation is None else (str(activation[0]), float(activation[1]), float(activation[2]))
+        self.shared_activation = None if shared_activation is None else (
+            str(shared_activation[0]), float(shared_activation[1]), float(shared_activation[2]))
+        self.shared_gated = bool(shared_gated)
         self.w_router = self.w_gate = self.w_up = self.w_down = None
         self.w_shared_gate_up = self.w_shared_down = None
 
@@ -43,7 +57,9 @@ class RoutedExperts(Part):
         if self.shared_size is not None:
             s = self.shared_size
             specs.update({"shared.gate": WeightSpec((s, h), MATRIX), "shared.up": WeightSpec((s, h), MATRIX),
-                          "shared.down": WeightSpec((h, s), MATRIX), "shared.sg": WeightSpec((1, h), MATRIX)})
+                          "shared.down": WeightSpec((h, s), MATRIX)})
+            if self.shared_gated:
+                specs["shared.sg"] = WeightSpec((1, h), MATRIX)
         return specs
 
     def load_weights(self, tensors, ops):
@@ -55,7 +71,8 @@ class RoutedExperts(Part):
 
         router = [tensors["router"]]
         if self.shared_size is not None:
-            router.append(tensors["shared.sg"])
+            if self.shared_gated:
+                router.append(tensors["shared.sg"])
             g, u = tensors["shared.gate"], tensors["shared.up"]
             if g.dtype != u.dtype:
                 g, u = g.to(torch.float32), u.to(torch.float32)
@@ -77,13 +94,22 @@ class RoutedExperts(Part):
         ids = torch.empty((t, self.top), dtype=torch.int32, device=h.device)
         weights = torch.empty((t, self.top), dtype=torch.float32, device=h.device)
         shared_gate = None
-        if self.shared_size is not None:
+        if self.shared_size is not None and self.shared_gated:
             shared_gate = torch.empty((t,), dtype=torch.float32, device=h.device)
-        ops.router_topk(logits, self.experts, self.top, ids, weights, shared_gate)
+        ops.router_topk(logits, self.experts, self.top, ids, weights, shared_gate, softmax=self.router == "softmax")
         shared = None
-        if self.shared_size is not None:
+        plain = self.activation is None and self.shared_activation is None and self.shared_gated
+        if self.shared_size is not None and plain:
             shared = (self.w_shared_gate_up, self.w_shared_down, shared_gate)
-        ops.routed_experts(h, self.w_experts, ids, weights, residual, shared)
+        ops.routed_experts(h, self.w_experts, ids, weights, residual, shared, act=self.activation)
+        if self.shared_size is not None and not plain:
+            # a shared expert with an activation of its own, or without a gate: a feed-forward beside the routed ones
+            kind, limit, alpha = self.shared_activation or ("silu", 0.0, 0.0)
+            if shared_gate is None:
+                ops.glu_ffn(h, self.w_shared_gate_up, self.w_shared_down, residual, kind, limit, alpha)
+            else:
+                ops.glu_ffn(h, self.w_shared_gate_up, self.w_shared_down, residual, kind, limit, alpha,
+                            row_scale=shared_gate)
 
 
 register_part("ffn", "routed_experts", RoutedExperts)

@@ -43,3 +43,42 @@ class RMSNorm(Part):
 
 
 register_part("norm", "rmsnorm", RMSNorm)
+
+
+class GroupRMSNorm(Part):
+    """RMS norm in groups: a row is cut into ``groups`` equal consecutive parts, each part is
+    divided by its own ``sqrt(mean(part^2) + eps)``, and the whole row is multiplied by a weight
+    per element.  ``groups = 1`` is the plain norm.  Besides the two forms every norm has,
+    ``add_to`` adds the normed rows to a float32 residual: blocks that norm a sublayer's output
+    rather than its input use it."""
+    category = "norm"
+
+    def __init__(self, size: int, eps: float, groups: int = 1, tensor: str = "weight"):
+        self.size, self.eps, self.groups = int(size), float(eps), int(groups)
+        if self.groups < 1 or self.size % self.groups:
+            raise ValueError(f"{self.size} elements do not fall into {self.groups} equal groups")
+        self.tensor = str(tensor)
+        self.weight: torch.Tensor | None = None
+
+    def weight_specs(self):
+        return {self.tensor: WeightSpec((self.size,), NORM_WEIGHT)}
+
+    def load_weights(self, tensors, ops):
+        self.weight = as_float32(tensors[self.tensor]).contiguous()
+
+    def forward(self, ops, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        out = torch.empty((x.shape[0], self.size), dtype=out_dtype, device=x.device)
+        ops.group_norm(x, self.weight, self.eps, self.groups, out=out)
+        return out
+
+    def forward_rows(self, ops, x: torch.Tensor, rows: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        out = torch.empty((rows.shape[0], self.size), dtype=out_dtype, device=x.device)
+        ops.group_norm(x, self.weight, self.eps, self.groups, out=out, rows=rows)
+        return out
+
+    def add_to(self, ops, y: torch.Tensor, residual: torch.Tensor) -> None:
+        """``residual += norm(y)``, both float32."""
+        ops.group_norm(y, self.weight, self.eps, self.groups, residual=residual)
+
+
+register_part("norm", "group_rmsnorm", GroupRMSNorm)

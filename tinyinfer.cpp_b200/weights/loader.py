@@ -44,7 +44,7 @@ def check_tensors(where: str, expected: Mapping[str, WeightSpec],
     def fits(want, have) -> bool:              # None in a wanted shape: the tensor decides that size
         return len(want) == len(have) and all(w is None or int(w) == int(h) for w, h in zip(want, have))
 
-    missing = [n for n in expected if n not in found]
+    missing = [n for n in expected if n not in found and not expected[n].optional]
     unexpected = [n for n in found if n not in expected and n not in duplicates]
     wrong = [(n, expected[n].shape, found[n]) for n in expected
              if n in found and not fits(expected[n].shape, found[n])]
@@ -86,7 +86,7 @@ def load_model_weights(model, model_dir: str, device, ops) -> None:
             t = index[name].get(name)
             return t.to(device=device, dtype=storage_dtype(t.dtype), copy=True)
 
-        model.load_weights(fetch, ops)
+        model.load_weights(fetch, ops, present=lambda name: name in index)
     finally:
         for f in files:
             f.close()
