@@ -9,18 +9,27 @@ from __future__ import annotations
 import json
 import math
 import os
+import struct
 
 import torch
-
-from tinyinfer_b200.weights.safetensors_io import read_safetensors
 
 F = torch.float64
 
 
 def load_folder(folder: str):
+    """Configuration and float64 tensors of a model folder, read with the standard library and torch alone."""
     with open(os.path.join(folder, "config.json")) as fh:
         cfg = json.load(fh)
-    weights = {k: v.to(F) for k, v in read_safetensors(os.path.join(folder, "model.safetensors")).items()}
+    kinds = {"BF16": torch.bfloat16, "F32": torch.float32, "F16": torch.float16, "I32": torch.int32}
+    with open(os.path.join(folder, "model.safetensors"), "rb") as fh:
+        (n,) = struct.unpack("<Q", fh.read(8))
+        header = json.loads(fh.read(n))
+        data = fh.read()
+    weights = {}
+    for name, ent in header.items():
+        if name != "__metadata__":
+            lo, hi = ent["data_offsets"]
+            weights[name] = torch.frombuffer(bytearray(data[lo:hi]), dtype=kinds[ent["dtype"]]).view(ent["shape"]).to(F)
     return cfg, weights
 
 
