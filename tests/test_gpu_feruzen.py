@@ -1,0 +1,641 @@
+"""Feruzen on the GPU against the plain implementation: every kernel alone, each mixer alone over
+requests cut into portions (also with inputs made so that one far write or one key carries the
+answer), whole prompts, the same requests cut in different ways, long decoding, reused pages and
+state slots, and greedy generation through the entry point.
+
+float32 is the sharp comparison.  A mechanism alone agrees to 2e-5 of its largest output; the
+whole model to 6e-5 of the largest logit, because the norm on every sublayer's output hands a
+sublayer's rounding on undamped (torch's own float32 run of the plain implementation is off by
+up to 1.6e-5 on these models).  In bfloat16 a mechanism alone agrees to 3e-2; in the whole model
+one expert chosen differently moves every later row through the recurrent states, so the bound is
+3e-2 for half the rows and 0.12 for nine out of ten."""
+import copy
+import json
+import os
+import subprocess
+import sys
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import plain_feruzen as plain
+import traces
+from feruzen_util import SMALL, glu_weights, make_model, mixer_weights, mlp_weights
+from util import assert_close_logits, random_tokens
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+MODEL_RTOL = 6e-5     # float32 engine against the float64 plain model, of the largest logit
+LENGTHS = {"A": [70, 45, 120, 33, 17, 2, 64, 1], "B": [40, 9, 130, 1], "C": [300, 33, 150, 64, 217, 17]}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tinyinfer_b200.kernels import cuda_ops
+    return cuda_ops(DEV)
+
+
+def _requests(name):
+    vocab = SMALL[name]["vocab"]
+    return {f"r{i}": random_tokens(vocab, n, seed=900 + i) for i, n in enumerate(LENGTHS[name])}
+
+
+_PLAIN = {}
+
+
+def _plain(model_dir, name):
+    if name not in _PLAIN:
+        cfg, w = plain.load_folder(model_dir)
+        _PLAIN[name] = {r: plain.forward(cfg, w, t) for r, t in _requests(name).items()}
+    return _PLAIN[name]
+
+
+def _run(model_dir, dtype, steps, max_tokens, page_size=16, max_requests=4):
+    from tinyinfer_b200 import Engine, StepEntry
+    eng = Engine(model_dir, dtype=dtype, page_size=page_size, num_pages=-(-max_tokens // page_size),
+                 max_requests=max_requests)
+    outputs = {}
+    for s in steps:
+        outputs[s["step"]] = eng.step([StepEntry(e["id"], e["tokens"], e["want"]) for e in s["entries"]]).cpu()
+        for r in s["end"]:
+            eng.finish(r)
+        eng.cache.check()
+    eng.ops.check_status()
+    assert eng.cache.free_pages() == [g.pool.count for g in eng.cache.groups], "pages were lost"
+    return outputs
+
+
+def _compare(steps, outputs, want, dtype, what):
+    for r, got in traces.collect(steps, outputs).items():
+        pos = [p for p, _ in got]
+        g = torch.stack([x for _, x in got])
+        ref = want[r][pos]
+        if dtype == "float32":
+            assert_close_logits(g, ref, MODEL_RTOL, f"{what} {r}")
+        else:
+            err = (g.double() - ref).abs().max(dim=-1).values / ref.abs().max()
+            assert torch.isfinite(g).all()
+            most = torch.quantile(err, 0.9) if len(err) >= 10 else err.median()
+            assert err.median() < 3e-2 and most < 0.12, \
+                f"{what} {r}: rows off by {err.topk(min(5, len(err))).values.tolist()}, median {float(err.median())}"
+
+
+def _rows_step(q_lens, slots):
+    """What the row kernels read of a step: which request a row belongs to, where portions start."""
+    ti = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    req = [r for r, n in enumerate(q_lens) for _ in range(n)]
+    return SimpleNamespace(req_of_tok=ti(req), cu_q=ti(cu), num_requests=len(q_lens), max_q_len=max(q_lens),
+                           scratch={}), ti(slots)
+
+
+# ---- kernels alone ---------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sizes", [(5, 48, 3), (1, 36, 1), (70, 256, 4), (9, 40, 40), (3, 2048, 2), (4, 66, 33)])
+def test_norm_in_groups(ops, sizes, dtype):
+    t, n, groups = sizes
+    g = torch.Generator().manual_seed(n)
+    x = torch.randn((t, n), generator=g) * torch.logspace(-2, 2, n)[None]      # groups of very different size
+    w = 1 + 0.3 * torch.randn((n,), generator=g)
+    want = plain.group_norm(x.double(), w.double(), groups, 1e-5)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    out = torch.empty((t, n), dtype=dtype, device=DEV)
+    ops.group_norm(x.to(DEV), w.to(DEV), 1e-5, groups, out=out)
+    assert ((out.cpu().double() - want).abs() / (1 + want.abs())).max() < tol
+    rows = torch.tensor([t - 1, 0], dtype=torch.int32, device=DEV)
+    some = torch.empty((2, n), dtype=dtype, device=DEV)
+    ops.group_norm(x.to(DEV), w.to(DEV), 1e-5, groups, out=some, rows=rows)
+    assert torch.equal(some, out[[t - 1, 0]])
+    res = torch.randn((t, n), generator=g)
+    acc = res.clone().to(DEV)
+    ops.group_norm(x.to(DEV), w.to(DEV), 1e-5, groups, residual=acc)
+    assert ((acc.cpu().double() - (res.double() + want)).abs() / (1 + want.abs())).max() < 1e-5
+
+
+@pytest.mark.parametrize("taps", [1, 2, 3, 4, 7])
+@pytest.mark.parametrize("options", [(False, False), (True, False), (False, True)])
+def test_time_convolution_over_portions(ops, taps, options):
+    """Three requests in portions as short as one row, shorter than the taps reach; slots in another
+    order than the requests; a slice of wider rows as input."""
+    add_input, silu = options
+    c = 40
+    g = torch.Generator().manual_seed(taps)
+    total = {"a": 23, "b": 9, "c": 14}
+    x = {r: torch.randn((n, c + 6), generator=g) for r, n in total.items()}
+    w = torch.randn((c, taps), generator=g)
+    slot = {"a": 2, "b": 0, "c": 1}
+    state = SimpleNamespace(state=torch.zeros((3, 5 + (taps - 1) * c), dtype=torch.float32, device=DEV), slots=None,
+                            writes=True)
+    cuts = [[("a", 1), ("b", 5)], [("a", 1), ("c", 2)], [("a", 2), ("b", 1), ("c", 1)], [("a", 12), ("b", 3), ("c", 11)],
+            [("a", 7)]]
+    at = {r: 0 for r in total}
+    got = {r: [] for r in total}
+    for cut in cuts:
+        step, state.slots = _rows_step([n for _, n in cut], [slot[r] for r, _ in cut])
+        rows = torch.cat([x[r][at[r]:at[r] + n] for r, n in cut]).to(DEV)
+        out = torch.empty((rows.shape[0], c), dtype=torch.float32, device=DEV)
+        ops.causal_conv(rows[:, 3:3 + c], w.to(DEV), step, state, 5, out, add_input=add_input, silu=silu)
+        ops.conv_tail_store(rows[:, 3:3 + c], taps, step, state, 5)
+        o = 0
+        for r, n in cut:
+            got[r].append(out[o:o + n].cpu())
+            at[r] += n
+            o += n
+    for r in total:
+        xs = x[r][:at[r], 3:3 + c].double()
+        want = plain.time_conv(xs, w.double()) + (xs if add_input else 0)
+        if silu:
+            want = plain.silu(want)
+        assert (torch.cat(got[r]).double() - want).abs().max() < 1e-5, r
+    assert state.state[:, :5].abs().max() == 0                      # what lies before the offset is left alone
+
+
+def test_depth_sum_and_scaled_sum(ops):
+    g = torch.Generator().manual_seed(0)
+    t, n, layers = 7, 48, 4
+    hist = torch.full((layers + 1, t, n), float("nan"), dtype=torch.float32, device=DEV)
+    results = [torch.randn((t, n), generator=g)]
+    x = results[0].clone().to(DEV)
+    ops.depth_mix(x, hist, 0)
+    assert torch.equal(x.cpu(), results[0])
+    for i in range(layers):
+        new = torch.randn((t, n), generator=g)                     # what layer i leaves
+        results.append(new)
+        w = torch.randn((i + 2,), generator=g)
+        x = new.clone().to(DEV)
+        ops.depth_mix(x, hist, i + 1, w.to(DEV))
+        want = sum(w[j].double() * results[j].double() for j in range(i + 2))
+        assert (x.cpu().double() - want).abs().max() < 1e-5
+    a, b = torch.randn((t, n), generator=g), torch.randn((t, n), generator=g)
+    wide = torch.zeros((t, n + 8), dtype=torch.float32, device=DEV)
+    dst = wide[:, 4:4 + n]
+    dst.copy_(results[0])
+    ops.add_scaled(dst, a.to(DEV), -0.5, b.to(DEV), 1.25)
+    assert (dst.cpu().double() - (results[0].double() - 0.5 * a.double() + 1.25 * b.double())).abs().max() < 1e-6
+    assert wide[:, :4].abs().max() == 0 and wide[:, 4 + n:].abs().max() == 0
+
+
+# ---- feed-forwards ---------------------------------------------------------------------------
+def _ffn_part(ops, mlp, width, w):
+    from tinyinfer_b200.config import feruzen
+    from tinyinfer_b200.parts.base import build_part
+    cfg = SimpleNamespace(width=width)
+    part = build_part("ffn", feruzen._ffn_spec(cfg, feruzen._mlp({"mlp": mlp}, "here")))
+    part.load_weights({k: v.to(DEV) for k, v in w.items()}, ops)
+    return part
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sizes", [(1, 48, 40, 1.5), (9, 36, 8, 0.25), (70, 128, 192, 2.0), (300, 64, 96, 7.0), (3, 40, 24, 1.0)])
+def test_clamped_feed_forward(ops, sizes, dtype):
+    """Inputs large enough that the gate reaches its upper clamp (and stays free below) and the other
+    branch both of its clamps."""
+    t, width, ff, limit = sizes
+    g = torch.Generator().manual_seed(ff)
+    w = glu_weights(width, ff, g)
+    h = (torch.randn((t, width), generator=g) * 1.5).to(dtype)
+    gate = h.double() @ w["gate"].double().T
+    assert (gate > limit).any() and (gate < -limit).any()
+    part = _ffn_part(ops, {"kind": "dense", "ff": ff, "limit": limit}, width, w)
+    res = torch.zeros((t, width), dtype=torch.float32, device=DEV)
+    part.forward(ops, h.to(DEV), res, None)
+    want = plain.clamped_glu(h.double(), w["gate"].double(), w["up"].double(), w["down"].double(), limit)
+    err = (res.cpu().double() - want).abs().max() / want.abs().max()
+    assert err < (2e-5 if dtype == torch.float32 else 2e-2), err
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sizes", [(5, 2, 24, 16), (4, 4, 8, None), (1, 1, 24, 8), (3, 1, 16, None), (16, 3, 32, None),
+                                   (8, 2, 64, 128), (12, 5, 16, 16), (40, 6, 16, None)])
+@pytest.mark.parametrize("t", [1, 7, 150])
+def test_softmax_router_and_experts(ops, sizes, t, dtype):
+    """The chosen experts' shares of the softmax over all experts weigh their outputs as they are
+    (they do not sum to one); a shared expert with a limit of its own is added for every row."""
+    experts, top, ff, shared = sizes
+    width = 64 if ff >= 32 else 48
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff, "limit": 1.25}}
+    if shared is not None:
+        mlp["shared"] = {"ff": shared, "limit": 0.5}
+    g = torch.Generator().manual_seed(experts * 10 + top)
+    w = mlp_weights(mlp, width, g)
+    h = torch.randn((t, width), generator=g).to(dtype)
+    part = _ffn_part(ops, mlp, width, w)
+    res = torch.zeros((t, width), dtype=torch.float32, device=DEV)
+    part.forward(ops, h.to(DEV), res, SimpleNamespace(scratch={}))
+    w64 = {"m." + k: v.double() for k, v in w.items()}
+    want = plain.feed_forward(w64, "m.", h.double(), mlp)
+    err = (res.cpu().double() - want).abs().max(dim=-1).values / want.abs().max()
+    # bfloat16: a row whose router scores lie within rounding of each other may choose another expert
+    bad = int((err > (2e-5 if dtype == torch.float32 else 3e-2)).sum())
+    assert bad <= (0 if dtype == torch.float32 else t // 20), err.topk(min(3, t)).values.tolist()
+
+
+# ---- mixers alone ----------------------------------------------------------------------------
+def _run_mixer(ops, part, inputs, cuts, dtype, page_size=16, max_requests=3):
+    """Run a mixer part over requests whose rows ``inputs[r]`` [T_r, width] arrive cut as ``cuts``
+    (a list of steps, each a list of (request, count); a count of 0 gives back what the request
+    holds); returns its output rows per request."""
+    from tinyinfer_b200.cache import CacheManager
+    from tinyinfer_b200.engine.batch import StepEntry, build_step_batch
+    width = next(iter(inputs.values())).shape[1]
+    lists = ops.step_lists(dtype) + list(part.step_lists())
+    cm = CacheManager([part.cache_spec()], page_size=page_size,
+                      num_pages=sum(-(-x.shape[0] // page_size) for x in inputs.values()) + 2,
+                      max_requests=max_requests, kv_dtype=dtype, device=DEV)
+    at = {r: 0 for r in inputs}
+    got = {r: [] for r in inputs}
+    for step_cuts in cuts:
+        for r, n in step_cuts:
+            if n == 0:
+                cm.free_request(r)
+        step_cuts = [(r, n) for r, n in step_cuts if n]
+        entries = [StepEntry(r, [0] * n, []) for r, n in step_cuts]
+        starts = cm.reserve_step([(r, n) for r, n in step_cuts])
+        tables = [[cm.block_table(g, r) for r, _ in step_cuts] for g in range(len(cm.groups))]
+        batch = build_step_batch(entries, starts, tables, [cm.state_slot(r) for r, _ in step_cuts], dtype, DEV,
+                                 lists=lists)
+        h = torch.cat([inputs[r][at[r]:at[r] + n] for r, n in step_cuts]).to(dtype).to(DEV)
+        residual = torch.zeros((h.shape[0], width), dtype=torch.float32, device=DEV)
+        part.forward(ops, h, residual, batch, cm.view(0, True, batch.block_tables, batch.state_slots))
+        ops.flush()
+        o = 0
+        for r, n in step_cuts:
+            got[r].append(residual[o:o + n].cpu())
+            at[r] += n
+            o += n
+            cm.release_passed(r)
+    ops.check_status()
+    return {r: torch.cat(v) for r, v in got.items()}
+
+
+def _mixer_part(ops, kind, m, width, w, eps=1e-5):
+    from tinyinfer_b200.config import feruzen
+    from tinyinfer_b200.parts.base import build_part
+    entry = {"type": kind, "mixer": m}
+    cfg = SimpleNamespace(width=width, norm_eps=eps)
+    layer = feruzen.FeruzenLayer(kind, feruzen._mixer(entry, "here", kind), None)
+    part = build_part("mixer", feruzen._mixer_spec(cfg, layer))
+    part.load_weights({k: v.to(DEV) for k, v in w.items()}, ops)
+    return part
+
+
+CUTS = [[("a", 30), ("b", 1)], [("b", 2), ("c", 5)], [("a", 1), ("b", 30), ("c", 1)], [("a", 2), ("c", 1)],
+        [("a", 17), ("b", 7), ("c", 33)], [("a", 1)], [("a", 1), ("c", 2)]]
+TOTAL = {"a": 52, "b": 40, "c": 42}
+
+
+def _delta(heads, kv_heads, dim, vdim, conv):
+    return "delta", {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv}
+
+
+def _sides(left, right, ls, rs):
+    h, g, d, dv, rot, base, scale = left
+    rh, rd, rdv, cap = right
+    return "parallel", {"left": {"heads": h, "kv_heads": g, "dim": d, "vdim": dv, "rot": {"dims": rot, "base": base},
+                                 "scale": scale},
+                        "right": {"heads": rh, "dim": rd, "vdim": rdv, "gate_cap": cap}, "left_scale": ls, "right_scale": rs}
+
+
+MIXER_CASES = [
+    _delta(4, 2, 8, 12, 3), _delta(1, 1, 16, 16, 1), _delta(2, 1, 64, 64, 4), _delta(3, 3, 40, 24, 2),
+    _delta(2, 2, 128, 160, 2), _delta(1, 1, 200, 96, 4), _delta(6, 2, 32, 48, 5),
+    _sides((4, 2, 12, 8, 6, 1000.0, 0.29), (3, 8, 12, 5.0), 0.7, 1.3),
+    _sides((2, 1, 64, 64, 64, 1e5, 0.12), (2, 64, 128, 10.0), 1.0, 1.0),
+    _sides((1, 1, 16, 16, 0, 7.0, 0.25), (1, 16, 16, 1.0), 0.0, 1.0),           # the matrix memory alone
+    _sides((3, 3, 8, 8, 2, 30.0, 0.35), (2, 24, 192, 20.0), -0.5, 0.9),         # value heads wider than one block
+    _sides((6, 1, 32, 16, 16, 50.0, 0.2), (1, 130, 40, 3.0), 1.0, 0.0),         # the attention alone
+]
+
+
+def _plain_mixer(kind, w, x, m, eps=1e-5):
+    w64 = {"x." + k: v.double() for k, v in w.items()}
+    fn = plain.gated_delta if kind == "delta" else plain.side_by_side
+    return fn(w64, "x.", x, m, eps)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kind,m", MIXER_CASES)
+def test_each_mixer_alone_in_portions(ops, kind, m, dtype):
+    width = 48
+    g = torch.Generator().manual_seed(len(json.dumps(m)))
+    w = mixer_weights(kind, m, width, g)
+    part = _mixer_part(ops, kind, m, width, w)
+    inputs = {r: torch.randn((n, width), generator=g) for r, n in TOTAL.items()}
+    got = _run_mixer(ops, part, inputs, CUTS, dtype)
+    for r, x in inputs.items():
+        want = _plain_mixer(kind, w, x.to(dtype).double(), m)
+        err = (got[r].double() - want).abs().max() / want.abs().max()
+        assert err < (2e-5 if dtype == torch.float32 else 3e-2), f"{kind} request {r}: {err}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kind,m", [_delta(2, 1, 64, 64, 4), _delta(1, 1, 32, 128, 2), _delta(2, 2, 128, 160, 3),
+                                    _sides((1, 1, 16, 16, 16, 100.0, 0.25), (2, 32, 64, 12.0), 0.8, 1.1),
+                                    _sides((1, 1, 16, 16, 16, 100.0, 0.25), (1, 64, 320, 6.0), 0.0, 1.0)])
+def test_recurrences_over_long_portions(ops, kind, m, dtype):
+    """Portions long enough that a head's state columns are cut over several blocks, between portions
+    that are not: the state passes from one form of the kernel to the other, and a state slot that a
+    finished request gave back starts at zero again."""
+    width = 64
+    g = torch.Generator().manual_seed(m.get("vdim", 1))
+    w = mixer_weights(kind, m, width, g)
+    part = _mixer_part(ops, kind, m, width, w)
+    inputs = {"a": torch.randn((203, width), generator=g), "b": torch.randn((72, width), generator=g)}
+    inputs["c"] = inputs["b"][:40] * 0.5
+    cuts = [[("a", 3)], [("a", 130)], [("a", 1), ("b", 70)], [("a", 69), ("b", 2)], [("a", 0), ("c", 2)], [("c", 38)]]
+    got = _run_mixer(ops, part, inputs, cuts, dtype, max_requests=2)
+    for r, x in inputs.items():
+        want = _plain_mixer(kind, w, x.to(dtype).double(), m)
+        err = (got[r].double() - want).abs().max() / want.abs().max()
+        assert err < (2e-5 if dtype == torch.float32 else 3e-2), f"request {r}: {err}"
+
+
+def test_many_requests_with_wide_value_heads(ops):
+    """More (request, head, column block) triples than the GPU holds at a time: a block that starts
+    late must still find the normaliser and the running maximum as the step before left them."""
+    kind, m = _sides((1, 1, 16, 16, 0, 10.0, 0.25), (4, 64, 320, 6.0), 0.0, 1.0)
+    width, n_req = 32, 48
+    g = torch.Generator().manual_seed(48)
+    w = mixer_weights(kind, m, width, g)
+    part = _mixer_part(ops, kind, m, width, w)
+    inputs = {f"r{i}": torch.randn((5, width), generator=g) for i in range(n_req)}
+    cuts = [[(r, 3) for r in inputs], [(r, 1) for r in inputs], [(r, 1) for r in inputs]]
+    got = _run_mixer(ops, part, inputs, cuts, torch.float32, max_requests=n_req)
+    for r, x in inputs.items():
+        want = _plain_mixer(kind, w, x.double(), m)
+        assert (got[r].double() - want).abs().max() / want.abs().max() < 2e-5, r
+
+
+# ---- inputs made so that one write or one key carries the answer -------------------------------
+@pytest.mark.parametrize("decoded", [False, True])
+@pytest.mark.parametrize("mode", ["delta", "gated_sum"])
+def test_a_far_write_is_read_back(ops, mode, decoded):
+    """Token 0 writes a one-hot value under a key of its own; 700 tokens with other keys follow, in
+    portions and (``decoded``) one by one; the last token asks for the first key.  Without decay the
+    value comes back whole; with a decay of e^-0.01 a token its size shows against the norm's eps."""
+    import math
+    heads, kv, dk, dv, t = 2, 1, 16, 8, 701
+    g = torch.Generator().manual_seed(1)
+    k = torch.zeros((t, kv * dk))
+    k[torch.arange(1, t), 1 + torch.arange(1, t) % (dk - 1)] = 3.0       # never the first key again
+    k[0, 0] = 5.0
+    q = k.clone()
+    q[-1] = 0
+    q[-1, 0] = 8.0
+    v = torch.randn((t, heads * dv), generator=g)
+    v[0] = 0
+    v[0, 3] = 1.0
+    v[0, dv + 5] = 1.0
+    ones, eps = torch.ones((dv,), device=DEV), 1e-6
+    for rate in (0.0, 0.01):
+        if mode == "delta":         # beta = 1; decay exp(-softplus(a)) = exp(-rate)
+            s0 = torch.full((t, heads), 30.0)
+            s1 = torch.full((t, heads), -40.0 if rate == 0 else math.log(math.expm1(rate)))
+            c0, c1, cap = torch.zeros(heads), torch.zeros(heads), 0.0
+        else:                        # input gate e^0; forget gate sigmoid(z) = exp(-rate)
+            s0 = torch.zeros((t, heads))
+            c0, c1, cap = torch.zeros(heads), torch.zeros(heads), 20.0
+            s1 = torch.full((t, heads), 100.0 if rate == 0 else cap * math.atanh(-math.log(math.expm1(rate)) / cap))
+        state = SimpleNamespace(state=torch.zeros((3, heads * dk * (dv + 1) + heads), dtype=torch.float32, device=DEV),
+                                slots=None, writes=True)
+        cuts = [300, 2, 348] + [1] * 51 if decoded else [129, 2, 570]
+        at, last = 0, None
+        for n in cuts:
+            step, state.slots = _rows_step([n], [1])
+            out = torch.empty((n, heads * dv), dtype=torch.float32, device=DEV)
+            dev = lambda x: x[at:at + n].contiguous().to(DEV)
+            ops.matrix_state(mode, dev(q), dev(k), dev(v), dev(s0), dev(s1), c0.to(DEV), c1.to(DEV), step, state, out,
+                             heads=heads, kv_heads=kv, dk=dk, dv=dv, eps=eps, norm_weight=ones, cap=cap)
+            at, last = at + n, out[-1].cpu().double().view(heads, dv)
+        assert at == t
+        if mode == "delta":          # unit keys: o = v0 e^(-rate 700) dk^-1/2
+            o = math.exp(-rate * (t - 1)) * dk ** -0.5
+        else:                        # o = S^T q / max(|n . q|, e^-m): with m = 0, n . q = e^(-rate 700) 8 dk^-1/2 5
+            nq = math.exp(-rate * (t - 1)) * 8.0 * dk ** -0.5 * 5.0
+            o = nq / (max(nq, 1.0) + 1e-6)
+        want = o / math.sqrt(o * o / dv + eps)
+        for head, col in ((0, 3), (1, 5)):
+            assert abs(float(last[head, col]) - want) < 2e-4 * max(1.0, want), (mode, rate, last[head], want)
+            rest = last[head].clone()
+            rest[col] = 0
+            assert rest.abs().max() < 1e-4
+    assert state.state[0].abs().max() == 0 and state.state[2].abs().max() == 0     # the other slots are untouched
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("decoded", [False, True])
+def test_one_key_stands_out(ops, decoded, dtype):
+    """The query points at one key, whose value is a one-hot row: the output says whether it was
+    seen.  Targets: the first tokens, keys on both sides of page borders, a key hundreds of positions
+    back, the query's own, and (in a portion) the key right after the query, which must not be seen."""
+    from test_gpu_ruvuvik import _fill, _paged
+    heads, kv, dk, dv, ps = 4, 2, 16, 32, 16
+    for pos, targets in ((700, [0, 1, 3, 15, 16, 17, 351, 352, 687, 688, 699, 700]), (16, [0, 15, 16]), (1, [0, 1]), (0, [0])):
+        ctx = pos + 1
+        for target in targets:
+            n = 1 if decoded else min(ctx, 40)
+            step, cache, bt, positions, req = _paged([ctx], [n], ps, kv * (dk + dv), dtype, seed=pos)
+            g = torch.Generator().manual_seed(target)
+            keys = torch.randn((ctx, kv, dk), generator=g) * 0.1
+            values = torch.zeros((ctx, kv, dv))
+            values[:, :, 1] = 1.0
+            values[target, :, :2] = torch.tensor([1.0, 0.0])
+            direction = torch.nn.functional.normalize(torch.randn((dk,), generator=g), dim=0)
+            keys[target] = direction * 8
+            _fill(cache, bt, [keys], [values], kv, dk, dv)
+            q = torch.randn((n, heads, dk), generator=g) * 0.1
+            q[-1] = direction * 8
+            if n > 1:
+                q[-2] = direction * 8                           # the row before: the target may lie ahead of it
+            out = torch.empty((n, heads * dv), dtype=dtype, device=DEV)
+            ops.attention_options(q.reshape(n, -1).to(dtype).to(DEV), step, cache, out, heads, kv, dk, dv, 1.0)
+            rows = out.float().view(n, heads, dv)
+            assert (rows[-1, :, 0] > 0.99).all(), f"query {pos}, key {target}: {rows[-1, :, 0].tolist()}"
+            if n > 1 and target == pos:
+                assert (rows[-2, :, 0] < 0.01).all(), f"query {pos - 1} saw key {target}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("geom", [(4, 2, 12, 8, 6, 8), (1, 1, 16, 16, 16, 16), (6, 3, 10, 24, 0, 16), (8, 1, 96, 96, 96, 16),
+                                  (2, 1, 64, 64, 32, 64)])
+def test_norm_per_head_rotation_and_store(ops, geom, dtype):
+    """Every query and key head normed by itself with one shared weight, then the first ``rot``
+    elements turned in neighbouring pairs; keys and values land in their pages."""
+    from test_gpu_ruvuvik import _paged
+    from tinyinfer_b200.parts.rope import NoPosition, RopeInterleaved
+    heads, kv, dk, dv, rot, ps = geom
+    ctx, ql = [37, 5, 300], [9, 5, 1]
+    step, cache, bt, positions, req = _paged(ctx, ql, ps, kv * (dk + dv), dtype)
+    g = torch.Generator().manual_seed(3)
+    t = len(positions)
+    nq, nk, nv = heads * dk, kv * dk, kv * dv
+    proj = torch.randn((t, nq + nk + nv + 5), generator=g) * torch.logspace(-1, 1, nq + nk + nv + 5)[None]
+    qw, kw = 1 + 0.3 * torch.randn((dk,), generator=g), 1 + 0.3 * torch.randn((dk,), generator=g)
+    rotation = (RopeInterleaved(dk, 777.0, rot) if rot else NoPosition()).rotation(DEV)
+    q_out = torch.empty((t, nq), dtype=dtype, device=DEV)
+    ops.qk_rownorm_rope_store(proj.to(DEV), qw.to(DEV), kw.to(DEV), 1e-5, rotation, step, cache, q_out, heads, kv, dk, dv,
+                              per_head=True)
+    p64, pos = proj.double(), torch.tensor(positions)
+    q_want = plain.turn_pairs(plain.unit_rms(p64[:, :nq].view(t, heads, dk), 1e-5) * qw.double(), pos, rot, 777.0)
+    k_want = plain.turn_pairs(plain.unit_rms(p64[:, nq:nq + nk].view(t, kv, dk), 1e-5) * kw.double(), pos, rot, 777.0)
+    v_want = p64[:, nq + nk:nq + nk + nv].view(t, kv, dv)
+    tol = 5e-5 if dtype == torch.float32 else 3e-2       # an angle of 300 in float32 is good to 2e-5
+    close = lambda got, want: ((got - want).abs() / (1 + want.abs())).max() < tol
+    assert close(q_out.cpu().double().view(t, heads, dk), q_want)
+    for i, (p, r) in enumerate(zip(positions, req)):
+        page = cache.pages[int(bt[r, p // ps])].cpu().double()
+        assert close(page[: kv * ps * dk].view(kv, ps, dk)[:, p % ps], k_want[i])
+        assert ((page[kv * ps * dk:].view(kv, ps, dv)[:, p % ps] - v_want[i]).abs() / (1 + v_want[i].abs())).max() < tol
+
+
+# ---- the model through the engine ------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_whole_prompts(tmp_path_factory, name, dtype):
+    d = make_model(tmp_path_factory.getbasetemp(), name)
+    steps = traces.whole(_requests(name))
+    out = _run(d, dtype, steps, traces.max_live_tokens(steps))
+    _compare(steps, out, _plain(d, name), dtype, f"{name} whole")
+
+
+def test_every_layer_against_the_plain_rows(tmp_path_factory):
+    """What each layer hands on, layer by layer, in float32: the first layer that differs names
+    the mechanism."""
+    from tinyinfer_b200 import Engine, StepEntry
+    for name in ("A", "C"):
+        d = make_model(tmp_path_factory.getbasetemp(), name)
+        cfg, w = plain.load_folder(d)
+        tokens = _requests(name)["r1"]
+        want = []
+        plain.forward(cfg, w, tokens, layer_rows=want)
+        eng = Engine(d, dtype="float32", page_size=16, num_pages=8, max_requests=1)
+        got = []
+        for block in eng.model.blocks:
+            inner = block.forward
+            block.forward = lambda ops, x, step, cache, inner=inner: (inner(ops, x, step, cache), got.append(x.clone()))[0]
+        eng.step([StepEntry("x", tokens, [0])])
+        assert len(got) == len(want)
+        for i, (a, b) in enumerate(zip(got, want)):
+            assert (a.cpu().double() - b).abs().max() < MODEL_RTOL * b.abs().max(), f"{name}: layer {i}"
+
+
+@pytest.mark.parametrize("name, family, dtype", [
+    ("A", "tail", "float32"), ("A", "portions", "float32"), ("A", "mixed", "float32"), ("A", "mixed", "bfloat16"),
+    ("B", "portions", "float32"), ("B", "mixed", "float32"), ("B", "tail", "bfloat16"),
+    ("C", "tail", "float32"), ("C", "portions", "bfloat16"), ("C", "mixed", "float32"), ("C", "mixed", "bfloat16"),
+    ("C", "long portions", "bfloat16"), ("C", "long portions", "float32")])
+def test_cuttings_agree_with_the_plain_implementation(tmp_path_factory, name, family, dtype):
+    """Prefill against token-by-token decoding, portions down to two tokens, and up to four live
+    requests of unequal length in a pool so small that pages and state slots are used again."""
+    d = make_model(tmp_path_factory.getbasetemp(), name)
+    reqs = _requests(name)
+    steps = {"tail": lambda: traces.tail_decoded(reqs, tail=40), "portions": lambda: traces.portions(reqs),
+             "long portions": lambda: traces.portions(reqs, sizes=(150, 2, 71, 70, 128, 3)),
+             "mixed": lambda: traces.mixed(reqs, seed=5)}[family]()
+    out = _run(d, dtype, steps, traces.max_live_tokens(steps))
+    _compare(steps, out, _plain(d, name), dtype, f"{name} {family}")
+
+
+def test_one_state_slot_used_by_every_request_in_turn(tmp_path_factory):
+    d = make_model(tmp_path_factory.getbasetemp(), "A")
+    steps = traces.portions(_requests("A"), sizes=(40, 2, 9))
+    out = _run(d, "float32", steps, traces.max_live_tokens(steps), max_requests=1)
+    _compare(steps, out, _plain(d, "A"), "float32", "one slot")
+
+
+def test_float32_cuttings_give_the_same_bits(tmp_path_factory):
+    d = make_model(tmp_path_factory.getbasetemp(), "A")
+    reqs = _requests("A")
+    seen = {}
+    for family in (traces.whole(reqs), traces.portions(reqs), traces.mixed(reqs, seed=2)):
+        out = _run(d, "float32", family, traces.max_live_tokens(family))
+        for r, rows in traces.collect(family, out).items():
+            for p, x in rows:
+                if (r, p) in seen:
+                    assert torch.equal(seen[(r, p)], x), f"request {r} position {p}"
+                seen[(r, p)] = x
+
+
+def test_long_decoding_and_pages_given_back(tmp_path_factory):
+    from tinyinfer_b200 import Engine, StepEntry
+    d = make_model(tmp_path_factory.getbasetemp(), "A")
+    tokens = random_tokens(SMALL["A"]["vocab"], 170, seed=77)
+    cfg, w = plain.load_folder(d)
+    want = plain.forward(cfg, w, tokens)
+    eng = Engine(d, dtype="float32", page_size=16, num_pages=11, max_requests=2)
+    got = [eng.step([StepEntry("x", tokens[:4], [3])])[0].cpu()]
+    for p in range(4, len(tokens)):
+        got.append(eng.decode_step([StepEntry("x", [tokens[p]], [0])])[0].cpu().clone())
+        eng.cache.check()
+    assert_close_logits(torch.stack(got), want[3:], MODEL_RTOL, "long decoding")
+    assert all(n == 0 for n in eng.cache.free_pages())              # 170 tokens hold all eleven pages of every group
+    eng.finish("x")
+    assert all(n == 11 for n in eng.cache.free_pages())
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(tmp_path_factory, name, graphs):
+    from tinyinfer_b200 import LLM, SamplingParams
+    d = make_model(tmp_path_factory.getbasetemp(), name)
+    cfg, w = plain.load_folder(d)
+    prompts = [random_tokens(cfg["vocab"], n, seed=n) for n in (5, 31, 12)]
+    llm = LLM(d, dtype="float32", max_seq=128, max_num_seqs=2, max_batched_tokens=24, page_size=16,
+              cuda_graph=graphs)
+    outs = llm.generate(prompts, SamplingParams(max_tokens=8))
+    for prompt, out in zip(prompts, outs):
+        assert out.tokens == plain.greedy(cfg, w, prompt, 8), f"prompt of {len(prompt)} tokens"
+
+
+def test_random_weights_from_a_configuration(tmp_path):
+    from tinyinfer_b200 import Engine, StepEntry, write_random_model
+    cfg = copy.deepcopy(SMALL["C"])
+    tokens = random_tokens(cfg["vocab"], 90, seed=1)
+    a = Engine(config=cfg, seed=5, dtype="bfloat16", page_size=16, num_pages=16, max_requests=2)
+    la = a.step([StepEntry("a", tokens, [0, 50, 89])])
+    d = os.path.join(str(tmp_path), "written")
+    write_random_model(d, cfg, seed=5)
+    b = Engine(d, dtype="bfloat16", page_size=16, num_pages=16, max_requests=2)
+    lb = b.step([StepEntry("a", tokens, [0, 50, 89])])
+    assert torch.isfinite(la).all() and torch.equal(la, lb)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_program(tmp_path_factory, tmp_path, dtype):
+    """The replay program as a user starts it: steps on standard input, logits in files."""
+    import numpy as np
+    d = make_model(tmp_path_factory.getbasetemp(), "C")
+    steps = traces.mixed(_requests("C"), seed=9)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = str(tmp_path / "out")
+    proc = subprocess.run(
+        [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", d, "--dtype", dtype, "--out", out,
+         "--max-tokens", str(traces.max_live_tokens(steps))],
+        input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [ln for ln in proc.stdout.splitlines() if ln.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    vocab = SMALL["C"]["vocab"]
+    outputs = {}
+    for s in steps:
+        wanted = sum(len(e["want"]) for e in s["entries"])
+        if wanted:
+            data = np.fromfile(os.path.join(out, f"{s['step']}.f32"), dtype="<f4")
+            outputs[s["step"]] = torch.from_numpy(data.reshape(wanted, vocab).copy())
+    _compare(steps, outputs, _plain(d, "C"), dtype, f"replay {dtype}")
+
+
+def test_command_line_with_token_ids(tmp_path_factory, capsys):
+    from tinyinfer_b200 import cli
+    d = make_model(tmp_path_factory.getbasetemp(), "B")
+    cfg, w = plain.load_folder(d)
+    prompt = random_tokens(cfg["vocab"], 9, seed=4)
+    rc = cli.main(["-m", d, "--tokens", "-p", " ".join(map(str, prompt)), "-n", "6", "--dtype", "float32",
+                   "--max-seq", "64", "--max-num-seqs", "2", "--page-size", "16"])
+    assert rc == 0
+    out = capsys.readouterr().out
+    line = [ln for ln in out.splitlines() if ln.startswith("[output]")][0]
+    assert [int(x) for x in line.split()[1:]] == plain.greedy(cfg, w, prompt, 6)

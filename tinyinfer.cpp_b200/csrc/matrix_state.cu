@@ -19,7 +19,10 @@
 // One block walks the tokens of one (request, head) in order.  A column of S belongs to four
 // neighbouring lanes, each holding a quarter of its rows in registers; a head's columns may be
 // cut over several blocks (few requests with long portions), which then write o as float32 and
-// leave the norm, the weight and the gate to `matrix_state_finish`.  Tokens are staged a tile at a
+// leave the norm, the weight and the gate to `matrix_state_finish`.  In the gated sum every such
+// block reads the normaliser's column and the running maximum, so their new values wait in
+// `carry` until all blocks are through and a small launch moves them into the slot (a block that
+// starts late must still find the old ones).  Tokens are staged a tile at a
 // time in shared memory; the per-token scalars (unit norms, beta, decays, gates) are made there
 // in parallel, the running maximum by one lane in order.  Everything is float32, and the order
 // of every sum depends on the sizes alone, so a row's bits depend neither on the batch nor on
@@ -48,6 +51,7 @@ struct MatrixStateArgs {
     int heads, kv_heads, dk, dv;
     void* out; int out_bf16;                              // [T, heads * dv] in the activation dtype (fused epilogue)
     float* o_raw;                                         // [T, heads * dv] float32 (columns cut over blocks)
+    float* carry;                                         // [requests, heads, dk + 1] float32 (columns cut, gated sum)
 };
 
 __device__ __forceinline__ float softplusf_(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
@@ -273,14 +277,36 @@ matrix_state_kernel(const MatrixStateArgs p) {
         }
     }
     __syncthreads();
+    float* carry = fused ? nullptr : p.carry + ((size_t)req * p.heads + head) * (dk + 1);
     if (live && (!is_norm_col || blockIdx.z == 0)) {
 #pragma unroll
         for (int ii = 0; ii < NI; ++ii) {
             const int i = (ii / 4) * (4 * LANES) + part * 4 + ii % 4;
-            if (i < dk) s_head[(size_t)i * cols + j] = S[ii];
+            if (i < dk) {
+                if (is_norm_col && !fused) carry[i] = S[ii];
+                else s_head[(size_t)i * cols + j] = S[ii];
+            }
         }
     }
-    if (MODE == MODE_GATED_SUM && tid == 0 && blockIdx.z == 0) *m_state = m_carry;
+    if (MODE == MODE_GATED_SUM && tid == 0 && blockIdx.z == 0) {
+        if (fused) *m_state = m_carry;
+        else carry[dk] = m_carry;
+    }
+}
+
+// The gated sum's normaliser column and running maximum from `carry` into the slots, after every
+// block of the cut launch has read the old ones: one block per (request, head).
+__global__ void __launch_bounds__(64)
+matrix_state_commit_kernel(const float* __restrict__ carry, const int* __restrict__ cu_q,
+                           const int* __restrict__ slots, float* state, long long state_stride, int heads, int dk,
+                           int dv) {
+    const int req = blockIdx.x, head = blockIdx.y;
+    if (cu_q[req] >= cu_q[req + 1]) return;
+    const int cols = dv + 1;
+    const float* c = carry + ((size_t)req * heads + head) * (dk + 1);
+    float* slot = state + (size_t)slots[req] * state_stride;
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) slot[((size_t)head * dk + i) * cols + dv] = c[i];
+    if (threadIdx.x == 0) slot[(size_t)heads * dk * cols + head] = c[dk];
 }
 
 // out[t, head] = o / rms(o) * weight * act(gate) for rows that column-cut blocks left as float32:
@@ -338,7 +364,7 @@ extern "C" int ti_matrix_state(int mode, const float* q, const float* k, const f
                                int gate_act, const float* norm_weight, int norm_per_row, float eps,
                                const int* cu_q, const int* slots, int requests, int rows, float* state,
                                long long state_stride, int heads, int kv_heads, int dk, int dv, int col_block,
-                               void* out, int out_dtype, float* o_raw, void* stream) {
+                               void* out, int out_dtype, float* o_raw, float* carry, void* stream) {
     if (requests == 0 || rows == 0) return 0;
     TI_REQUIRE(mode == MODE_DELTA || mode == MODE_GATED_SUM, "matrix_state: mode %d", mode);
     TI_REQUIRE(dk >= 1 && dk <= 256 && dv >= 1 && dv <= 1024, "matrix_state: head sizes %d x %d (keys up to 256, "
@@ -350,6 +376,8 @@ extern "C" int ti_matrix_state(int mode, const float* q, const float* k, const f
                "matrix_state: %d columns a block", col_block);
     TI_REQUIRE(col_block != 0 || dv <= 128, "matrix_state: %d value columns do not fit one block", dv);
     TI_REQUIRE(col_block == 0 || o_raw != nullptr, "matrix_state: cut columns need the float32 rows");
+    TI_REQUIRE(col_block == 0 || mode != MODE_GATED_SUM || carry != nullptr,
+               "matrix_state: cut columns of the gated sum need room for the normaliser and the maximum");
     MatrixStateArgs a;
     a.q = q; a.k = k; a.v = v; a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride;
     a.s0 = s0; a.s1 = s1; a.s0_stride = s0_stride; a.s1_stride = s1_stride; a.c0 = c0; a.c1 = c1; a.cap = cap;
@@ -357,7 +385,7 @@ extern "C" int ti_matrix_state(int mode, const float* q, const float* k, const f
     a.norm_weight = norm_weight; a.norm_per_row = norm_per_row; a.eps = eps;
     a.cu_q = cu_q; a.slots = slots; a.state = state; a.state_stride = state_stride;
     a.heads = heads; a.kv_heads = kv_heads; a.dk = dk; a.dv = dv;
-    a.out = out; a.out_bf16 = out_dtype == TI_BF16; a.o_raw = o_raw;
+    a.out = out; a.out_bf16 = out_dtype == TI_BF16; a.o_raw = o_raw; a.carry = carry;
     cudaStream_t s = (cudaStream_t)stream;
     int cb = col_block, col_blocks = 1;
     if (cb == 0) cb = dv <= 32 ? 32 : dv <= 64 ? 64 : 128;
@@ -366,6 +394,11 @@ extern "C" int ti_matrix_state(int mode, const float* q, const float* k, const f
     else launch_dk<MODE_GATED_SUM>(a, requests, cb, col_blocks, s);
     if (int rc = ti_check_launch("matrix_state")) return rc;
     if (col_block != 0) {
+        if (mode == MODE_GATED_SUM) {
+            matrix_state_commit_kernel<<<dim3(requests, heads), 64, 0, s>>>(carry, cu_q, slots, state, state_stride,
+                                                                            heads, dk, dv);
+            if (int rc = ti_check_launch("matrix_state_commit")) return rc;
+        }
         const int blocks = (rows * heads + 7) / 8;
         if (out_dtype == TI_BF16)
             matrix_state_finish_kernel<bf16><<<blocks, 256, 0, s>>>(o_raw, norm_weight, norm_per_row, eps, gate,

@@ -57,7 +57,7 @@ class StateOps:
             b.ti_glu_rows.argtypes = [_vp, _i, _i, _i, _i, _f, _f, _vp, _i, _vp]
             b.ti_matrix_state.argtypes = [_i, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _f, _vp, _i, _i,
                                           _vp, _i, _f, _vp, _vp, _i, _i, _vp, _ll, _i, _i, _i, _i, _i, _vp, _i, _vp,
-                                          _vp]
+                                          _vp, _vp]
             self._state_lib = b
         return self._state_lib
 
@@ -190,7 +190,7 @@ class StateOps:
         self._want(out.is_contiguous() and tuple(out.shape) == (t, heads * dv), "matrix_state: out")
         self._want(state.writes, "matrix_state: a recurrence renews its state")
         # few (request, head) pairs with long portions: a head's columns over several blocks
-        col_block, o_raw = 0, None
+        col_block, o_raw, carry = 0, None, None
         pairs = step.num_requests * heads
         if dv > 128 or (self.cut_state_columns and dv >= 64 and step.max_q_len > 64 and 2 * pairs <= self.num_sms):
             col_block = 32
@@ -198,10 +198,13 @@ class StateOps:
                 col_block *= 2
             o_raw = torch.empty((t, heads * dv), dtype=torch.float32, device=q.device)
             self.launches += 1
+            if mode == "gated_sum":
+                carry = torch.empty((pairs, dk + 1), dtype=torch.float32, device=q.device)
+                self.launches += 1
         self._st(self.state_lib.ti_matrix_state(
             STATE_MODES[mode], q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0),
             s0.data_ptr(), s0.stride(0), s1.data_ptr(), s1.stride(0), c0.data_ptr(), c1.data_ptr(), float(cap),
             _ptr(gate), gate.stride(0) if gate is not None else 0, GATE_ACTS[gate_act], norm_weight.data_ptr(),
             int(bool(norm_per_row)), float(eps), step.cu_q.data_ptr(), state.slots.data_ptr(), step.num_requests, t,
             st.data_ptr(), st.stride(0), heads, kv_heads, dk, dv, col_block, out.data_ptr(), _CODE[out.dtype],
-            _ptr(o_raw), self._stream()))
+            _ptr(o_raw), _ptr(carry), self._stream()))
