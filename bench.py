@@ -677,6 +677,134 @@ def ruvuvik_arm(args) -> int:
     return 0
 
 
+# ---- the Feruzen decoder beside the Ruvuvik decoder at equal sizes ------------------------------
+# (width, attention heads, kv heads, head size, delta heads, delta key heads, delta key size, delta value size,
+#  memory heads, memory key size, memory value size, dense ff, experts, top, expert ff, shared ff, blocks of
+#  [delta + dense, side by side + experts, side by side + dense] layers)
+FERUZEN_SIZES = {
+    "w1024": (1024, 16, 4, 64, 8, 4, 64, 128, 4, 64, 128, 2816, 16, 2, 704, 1408, 2),
+    "w2048": (2048, 16, 4, 128, 16, 8, 128, 128, 8, 128, 128, 5632, 32, 4, 704, 2816, 2),
+    "w4096": (4096, 32, 8, 128, 32, 16, 128, 128, 8, 128, 512, 11008, 64, 4, 1408, 5632, 1),
+}
+
+
+def feruzen_config(size):
+    w, h, g, d, dh, dg, dd, dv, mh, md, mv, ff, experts, top, eff, sff, blocks = size
+    delta = {"type": "delta", "mixer": {"heads": dh, "kv_heads": dg, "dim": dd, "vdim": dv, "conv": 4}}
+    sides = {"type": "parallel", "mixer": {
+        "left": {"heads": h, "kv_heads": g, "dim": d, "vdim": d, "rot": {"dims": d, "base": 500000.0}, "scale": d ** -0.5},
+        "right": {"heads": mh, "dim": md, "vdim": mv, "gate_cap": 15.0}, "left_scale": 1.0, "right_scale": 1.0}}
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": eff, "limit": 7.0},
+           "shared": {"ff": sff, "limit": 7.0}}
+    layers = [dict(delta, mlp=dense), dict(sides, mlp=moe), dict(sides, mlp=dense)]
+    return {"architecture": "Feruzen", "vocab": DESIGN_VOCAB, "width": w, "norm": {"eps": 1e-6, "groups": 4},
+            "canon": {"taps": 4}, "layers": layers * blocks}
+
+
+def feruzen_arm(args) -> int:
+    """Prefill and decode throughput of the Feruzen decoder at sizes of real layers, beside the
+    Ruvuvik decoder (the closest design the engine has: attention with options and a recurrent mixer
+    with a matrix state) with as many layers of the same width, attention heads and head size, and
+    the time the device spends in every kind of kernel call per layer, with the fraction of the
+    roofline for the calls that have one."""
+    import torch
+    from tinyinfer_b200 import Engine, StepEntry
+    pk, pk_kind = peaks()
+    prompt_len, batch, context = args.prefill_tokens, args.batch, args.context
+    warmup = max(args.warmup, 3)
+    out = {"design": "feruzen", "beside": "ruvuvik at equal sizes", "peaks": pk_kind, "prefill_tokens": prompt_len,
+           "decode_batch": batch, "decode_context": context, "dtype": "bf16", "data": "synthetic", "sizes": {}}
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, DESIGN_VOCAB, (prompt_len,), generator=g).tolist()
+    hbm, tc = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    for key, size in FERUZEN_SIZES.items():
+        if args.design_size and key != args.design_size:
+            continue
+        w, h, kvh, d, dh, dg, dd, dv, mh, md, mv, ff, experts, top, eff, sff, blocks = size
+        beside = (w, h, kvh, d, max(context, prompt_len) + 64, 512, 64, 64, ff, blocks)
+        res = {}
+        calls = {"feruzen": ["attention_options", "qk_rownorm_rope_store", "matrix_state", "causal_conv", "conv_tail_store",
+                             "group_norm", "depth_mix", "add_scaled", "glu_ffn", "glu_rows", "router_topk", "routed_experts", "linear"],
+                 "ruvuvik": ["attention_options", "qk_rownorm_rope_store", "latent_prepare", "head_project",
+                             "token_shift_mix", "wkv_recurrence", "tanh_rows", "linear_xielu", "xielu_rows", "linear", "rmsnorm"]}
+        for arm, cfg in (("feruzen", feruzen_config(size)), ("ruvuvik", ruvuvik_config(beside))):
+            engine = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=args.page_size,
+                            num_pages=-(-max(batch * context, prompt_len) // args.page_size) + batch + 2,
+                            max_requests=batch + 1, step_graphs=True)
+            pf_ms = measure_prefill(engine, prompt_len, max(1, min(args.steps, 6)), torch)
+            ms, clocks, launches = measure_decode(engine, batch, context, args.steps, warmup, torch)
+            a = {"prefill_tok_s": round(prompt_len / pf_ms * 1e3), "prefill_ms": round(pf_ms, 3),
+                 "decode_tok_s": round(batch / ms * 1e3, 1), "decode_ms_per_step": round(ms, 4),
+                 "decode_launches_per_step": launches // max(1, args.steps), "clocks": clocks}
+            engine._step_graphs = None
+            engine.ops.fuse_decode_tail = engine.ops.fuse_decode_ffn = False   # every call of its own
+            names = calls[arm]
+            for _ in range(2):        # the first eager step sizes the allocator's pool; the second is read
+                spans = timed_ops(engine, names, lambda: engine.step([StepEntry("p", prompt, [prompt_len - 1])]), torch)
+                engine.finish("p")
+            ids = fill_requests(engine, batch, context - 4, torch)
+            for _ in range(2):
+                dspans = timed_ops(engine, names, lambda: engine.step([StepEntry(r, [1], [0]) for r in ids]), torch)
+            for r in ids:
+                engine.finish(r)
+            n_layers = 3 * blocks
+            a["calls_us"] = {
+                "prompt": {n: [round(x * 1e3, 1) for x in v[:12]] for n, v in spans.items() if not n.startswith("_") and n != "linear"},
+                "decode": {n: [round(x * 1e3, 1) for x in v[:12]] for n, v in dspans.items() if not n.startswith("_") and n != "linear"}}
+            a["per_layer_us"] = {
+                "prompt": {n: round(sum(v) / n_layers * 1e3, 1) for n, v in spans.items() if not n.startswith("_")},
+                "decode": {n: round(sum(v) / n_layers * 1e3, 1) for n, v in dspans.items() if not n.startswith("_")}}
+            seen_all = prompt_len * (prompt_len + 1) / 2
+
+            def frac(amount, ms_, peak):
+                return round(amount / (ms_ * 1e-3) / peak, 4)
+
+            if arm == "feruzen":
+                # calls in layer order: the delta layer's recurrence first, then the memories of the two side-by-side layers
+                st, dst = spans["matrix_state"], dspans["matrix_state"]
+                att, datt = spans["attention_options"], dspans["attention_options"]
+                # a prompt's recurrence reads q, k, v, the gate (float32) and two scalars a head, and writes a row;
+                # a decoding step reads and writes every request's state
+                delta_rows = prompt_len * ((2 * dg * dd + 2 * dh * dv + 2 * dh) * 4 + dh * dv * 2.0)
+                mem_rows = prompt_len * ((2 * mh * md + 2 * mh * mv + 2 * mh) * 4 + mh * mv * 2.0)
+                # the feed-forwards: a prompt's useful flops; a decoding step's weight bytes (experts: those that are hit)
+                ffn = {"prompt": spans["glu_ffn"][0], "decode": dspans["glu_ffn"][0]}      # the first layer's dense one
+                a["roofline_frac"] = {
+                    "prompt_attention": frac(4.0 * h * d * seen_all, att[0], tc),
+                    "decode_attention": frac(batch * kvh * context * 2 * d * 2.0, datt[0], hbm),
+                    "prompt_delta_rule_bytes": frac(delta_rows, st[0], hbm),
+                    "prompt_matrix_memory_bytes": frac(mem_rows, st[1], hbm),
+                    "decode_delta_rule_state_bytes": frac(batch * dh * dd * dv * 8.0, dst[0], hbm),
+                    "decode_matrix_memory_state_bytes": frac(batch * mh * md * (mv + 1) * 8.0, dst[1], hbm),
+                    "prompt_dense_ffn": frac(2.0 * prompt_len * 3 * w * ff, ffn["prompt"], tc),
+                    "decode_dense_ffn": frac(2.0 * 3 * w * ff, ffn["decode"], hbm),
+                    "prompt_experts": frac(2.0 * prompt_len * top * 3 * w * eff, spans["routed_experts"][0], tc),
+                    "decode_experts": frac(2.0 * 3 * w * eff * min(experts, batch * top), dspans["routed_experts"][0], hbm)}
+            else:
+                att, datt = spans["attention_options"], dspans["attention_options"]
+                rd = 64
+                # the first layer's feed-forward: the product with the activation, and the first product back to the width
+                ffn = {n: sp["linear_xielu"][0] + next(ms_ for ms_, (shape, acc) in zip(sp["linear"], sp["_linear_kinds"])
+                                                       if shape == (w, ff))
+                       for n, sp in (("prompt", spans), ("decode", dspans))}
+                a["roofline_frac"] = {
+                    "prompt_attention": frac(4.0 * h * d * seen_all, att[0], tc),
+                    "decode_attention": frac(batch * kvh * context * 2 * d * 2.0, datt[0], hbm),
+                    "prompt_recurrence_bytes": frac(prompt_len * w * (5 * 4 + 2.0), spans["wkv_recurrence"][0], hbm),
+                    "decode_recurrence_state_bytes": frac(batch * (w // rd) * rd * rd * 8.0, dspans["wkv_recurrence"][0], hbm),
+                    "prompt_dense_ffn": frac(2.0 * prompt_len * 2 * w * ff, ffn["prompt"], tc),
+                    "decode_dense_ffn": frac(2.0 * 2 * w * ff, ffn["decode"], hbm)}
+            res[arm] = a
+            del engine
+            torch.cuda.empty_cache()
+        out["sizes"][key] = {"width": w, "heads": h, "kv_heads": kvh, "head_dim": d, "delta": [dh, dg, dd, dv],
+                             "memory": [mh, md, mv], "ff": ff, "experts": experts, "top": top, "expert_ff": eff,
+                             "shared_ff": sff, "layers": 3 * blocks, **res}
+    print(json.dumps(out))
+    return 0
+
+
 def reference_binary():
     """The reference's command-line program, built with its own CMakeLists if it is not there yet.
     Returns (path, None) or (None, why not)."""
@@ -828,9 +956,9 @@ def main() -> int:
                     help="with --only mixed: the number of decoding requests beside the 512-token portion")
     ap.add_argument("--attention-in-turn", action="store_true",
                     help="with --only mixed: flash-decoding behind the prompt attention kernel, not beside it")
-    ap.add_argument("--design", choices=["kagorax", "ruvuvik"], default=None,
-                    help="set this decoder beside the Qwen3 decoder at equal sizes instead of the default run")
-    ap.add_argument("--design-size", choices=sorted(set(DESIGN_SIZES) | set(RUVUVIK_SIZES)), default=None,
+    ap.add_argument("--design", choices=["kagorax", "ruvuvik", "feruzen"], default=None,
+                    help="set this decoder beside the closest one the engine has (Qwen3; for feruzen: Ruvuvik) at equal sizes instead of the default run")
+    ap.add_argument("--design-size", choices=sorted(set(DESIGN_SIZES) | set(RUVUVIK_SIZES) | set(FERUZEN_SIZES)), default=None,
                     help="one of the sizes only")
     ap.add_argument("--only", choices=["decode", "prefill", "chains", "mixed"], default=None,
                     help="run one part only and print a short line (for profiling small cases)")
@@ -844,6 +972,8 @@ def main() -> int:
     warmup = max(args.warmup, 3)
     if args.design == "ruvuvik":
         return ruvuvik_arm(args)
+    if args.design == "feruzen":
+        return feruzen_arm(args)
     if args.design:
         return design_arm(args)
 
