@@ -718,6 +718,10 @@ def feruzen_arm(args) -> int:
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, DESIGN_VOCAB, (prompt_len,), generator=g).tolist()
     hbm, tc = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    # float32 multiply-adds on the CUDA cores (128 lanes an SM, the clock's maximum): what a walk over a float32 state
+    # is held against besides its bytes, since every state element takes a few of them per token
+    props = torch.cuda.get_device_properties(0)
+    fp32 = props.multi_processor_count * 128 * 2.0 * getattr(props, "clock_rate", 1965000) * 1e3
     for key, size in FERUZEN_SIZES.items():
         if args.design_size and key != args.design_size:
             continue
@@ -775,6 +779,9 @@ def feruzen_arm(args) -> int:
                     "decode_attention": frac(batch * kvh * context * 2 * d * 2.0, datt[0], hbm),
                     "prompt_delta_rule_bytes": frac(delta_rows, st[0], hbm),
                     "prompt_matrix_memory_bytes": frac(mem_rows, st[1], hbm),
+                    # per state element and token: the delta rule 3 multiply-adds and a product, the memory 2 and a product
+                    "prompt_delta_rule_fp32": frac(prompt_len * dh * dd * dv * 7.0, st[0], fp32),
+                    "prompt_matrix_memory_fp32": frac(prompt_len * mh * md * (mv + 1) * 5.0, st[1], fp32),
                     "decode_delta_rule_state_bytes": frac(batch * dh * dd * dv * 8.0, dst[0], hbm),
                     "decode_matrix_memory_state_bytes": frac(batch * mh * md * (mv + 1) * 8.0, dst[1], hbm),
                     "prompt_dense_ffn": frac(2.0 * prompt_len * 3 * w * ff, ffn["prompt"], tc),
@@ -792,6 +799,8 @@ def feruzen_arm(args) -> int:
                     "prompt_attention": frac(4.0 * h * d * seen_all, att[0], tc),
                     "decode_attention": frac(batch * kvh * context * 2 * d * 2.0, datt[0], hbm),
                     "prompt_recurrence_bytes": frac(prompt_len * w * (5 * 4 + 2.0), spans["wkv_recurrence"][0], hbm),
+                    # per state element and token: 3 multiply-adds
+                    "prompt_recurrence_fp32": frac(prompt_len * (w // rd) * rd * rd * 6.0, spans["wkv_recurrence"][0], fp32),
                     "decode_recurrence_state_bytes": frac(batch * (w // rd) * rd * rd * 8.0, dspans["wkv_recurrence"][0], hbm),
                     "prompt_dense_ffn": frac(2.0 * prompt_len * 2 * w * ff, ffn["prompt"], tc),
                     "decode_dense_ffn": frac(2.0 * 2 * w * ff, ffn["decode"], hbm)}

@@ -16,24 +16,29 @@
 // element of a head, or one per element of the row) and by act(gate) (silu or sigmoid), and write
 // the row in the activation dtype.
 //
-// One block walks the tokens of one (request, head) in order.  A column of S belongs to four
-// neighbouring lanes, each holding a quarter of its rows in registers; a head's columns may be
-// cut over several blocks (few requests with long portions), which then write o as float32 and
-// leave the norm, the weight and the gate to `matrix_state_finish`.  In the gated sum every such
-// block reads the normaliser's column and the running maximum, so their new values wait in
-// `carry` until all blocks are through and a small launch moves them into the slot (a block that
-// starts late must still find the old ones).  Tokens are staged a tile at a
-// time in shared memory; the per-token scalars (unit norms, beta, decays, gates) are made there
-// in parallel, the running maximum by one lane in order.  Everything is float32, and the order
-// of every sum depends on the sizes alone, so a row's bits depend neither on the batch nor on
-// how a prompt was cut.
+// One block walks the tokens of one (request, head) in order.  A column of S is spread over the rows:
+// sixteen "virtual lanes" each own four rows of every 64 (rows 64 g + 4 lane + 0..3), and a sum over
+// the rows is always taken per virtual lane first and then over the lanes as a tree of pairs
+// (lane ^ 1, ^ 2, ^ 4, ^ 8).  A thread plays four virtual lanes when a head's columns sit in one
+// block (4 threads a column, up to 128 columns), or one when the columns are cut over several blocks
+// (16 threads a column, 8 to 32 columns a block: few requests with long portions, where the walk is
+// bound by the instructions a warp issues per token); the bits are the same either way.  Blocks of
+// cut columns write o as float32 and leave the norm, the weight and the gate to
+// `matrix_state_finish`.  In the gated sum every such block reads the normaliser's column and the
+// running maximum, so their new values wait in `carry` until all blocks are through and a small
+// launch moves them into the slot (a block that starts late must still find the old ones).
+// Tokens are staged a tile at a time in shared memory, the next tile travelling by cp.async while
+// this one is worked; the per-token scalars (unit norms, beta, decays, gates) are made there in
+// parallel, the running maximum by one lane in order.  The unit norms of q and k and dk^-1/2 are
+// applied to the sums, not to the staged rows.  Everything is float32, and the order of every sum
+// depends on the sizes alone, so a row's bits depend neither on the batch nor on how a prompt was cut.
 #include "common.cuh"
 
 namespace {
 
 enum { MODE_DELTA = 0, MODE_GATED_SUM = 1 };
 enum { GATE_SILU = 0, GATE_SIGMOID = 1 };
-constexpr int LANES = 4;
+constexpr int VLANES = 16;               // virtual lanes of a column: the order of its sums is theirs
 
 struct MatrixStateArgs {
     const float* q; const float* k; const float* v;      // [T, .] float32 rows
@@ -52,6 +57,8 @@ struct MatrixStateArgs {
     void* out; int out_bf16;                              // [T, heads * dv] in the activation dtype (fused epilogue)
     float* o_raw;                                         // [T, heads * dv] float32 (columns cut over blocks)
     float* carry;                                         // [requests, heads, dk + 1] float32 (columns cut, gated sum)
+    int vec4;                                             // q, k, v rows and the heads in them start on 16 bytes
+    int cut;                                              // a head's columns lie over several blocks
 };
 
 __device__ __forceinline__ float softplusf_(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
@@ -61,82 +68,168 @@ __device__ __forceinline__ float gate_value(float g, int act) {
     return act == GATE_SILU ? g * s : s;
 }
 
+// Tokens a tile: two buffers of k and q rows and of v's columns (one is read while cp.async fills the
+// other) and one of o must fit the 48 KB of static shared memory.
 template <int DMAX, int CB> struct TileTokens {
-    static constexpr int value = (2 * DMAX + 2 * (CB + 1)) * 16 * 4 <= 40 * 1024 ? 16 : 8;
+    static constexpr int value = (4 * DMAX + 3 * (CB + 1)) * 16 * 4 <= 46 * 1024 ? 16 : 8;
 };
 
-template <int MODE, int DMAX, int CB>
-__global__ void __launch_bounds__(LANES * CB + (MODE == MODE_GATED_SUM ? 32 : 0))
+// 4 bytes from global to shared memory behind the thread's back; zeros where `valid` is false
+__device__ __forceinline__ void cp_async4(float* dst, const float* src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async16(float* dst, const float* src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::); }
+
+// The sum of a thread's VPT virtual lanes (neighbours first), then over the threads of a column.
+template <int VPT, int LANES> __device__ __forceinline__ float lanes_sum(const float (&x)[VPT]) {
+    float r = x[0];
+    if (VPT == 4) r = (x[0] + x[1]) + (x[2] + x[3]);
+#pragma unroll
+    for (int sh = 1; sh < LANES; sh *= 2) r += __shfl_xor_sync(0xffffffffu, r, sh);
+    return r;
+}
+
+// Small blocks of cut columns share an SM (the registers of at least 768 threads fit), so that other warps issue
+// while one waits on its sums.
+template <int MODE, int CB, int LANES> struct StateBlock {
+    // columns a thread holds (a k or q read serves them all): two for the cut columns halved the warps that
+    // hide one another's waits and was slower (2,048 tokens, 8 heads of 64 x 128: 460 -> 570 us)
+    static constexpr int cpt = 1;
+    static constexpr int threads = LANES * (CB / cpt) + (MODE == MODE_GATED_SUM ? 32 : 0);
+    static constexpr int resident = LANES == 16 && 768 / threads > 0 ? 768 / threads : 1;
+};
+
+template <int MODE, int DMAX, int CB, int LANES>
+__global__ void __launch_bounds__(StateBlock<MODE, CB, LANES>::threads, StateBlock<MODE, CB, LANES>::resident)
 matrix_state_kernel(const MatrixStateArgs p) {
     constexpr int TT = TileTokens<DMAX, CB>::value;
-    constexpr int NI = DMAX / LANES;                      // state rows per thread
-    constexpr int CS = CB + 1;                            // staged columns (the last: the normaliser's value 1)
-    constexpr int THREADS = LANES * CB + (MODE == MODE_GATED_SUM ? 32 : 0);
-    __shared__ __align__(16) float ks[TT][DMAX], qs[TT][DMAX];
-    __shared__ float vs[TT][CS], os[TT][CS];
-    __shared__ float sa[TT], sb[TT], sm[TT], inv_s[TT], m_carry;
+    constexpr int VPT = VLANES / LANES;                   // virtual lanes a thread plays: 4 or 1
+    constexpr int NG = DMAX / 64;                         // groups of 64 rows
+    constexpr int NI = NG * VPT * 4;                      // state rows per thread
+    constexpr int CS = CB + 1;                            // columns of o (the last: the normaliser's)
+    constexpr int CPT = StateBlock<MODE, CB, LANES>::cpt;
+    constexpr int GROUPS = CB / CPT;                      // threads along the columns
+    constexpr int THREADS = StateBlock<MODE, CB, LANES>::threads;
+    static_assert(DMAX % 64 == 0 && (VPT == 1 || VPT == 4) && THREADS >= 8 * TT && CB % 4 == 0 && CB % CPT == 0, "sizes");
+    __shared__ __align__(16) float ks_[2][TT][DMAX];
+    __shared__ __align__(16) float qs_[2][TT][DMAX];
+    __shared__ __align__(16) float vs_[2][TT][CB];
+    __shared__ float os[TT][CS];
+    __shared__ float s0s[2][TT], s1s[2][TT];
+    __shared__ float sa[TT], sb[TT], sfk[TT], sfq[TT], sm[TT], inv_s[TT], m_carry;
     const int req = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
     const int c0 = blockIdx.z * CB;
-    const int jc = tid / LANES, part = tid % LANES;       // column of this block, quarter of its rows
+    const int jc = tid / LANES, part = tid % LANES;       // column group of this block, share of its rows
     const int dk = p.dk, dv = p.dv;
     const int cols = dv + (MODE == MODE_GATED_SUM ? 1 : 0);              // columns of the stored state
-    const bool is_norm_col = MODE == MODE_GATED_SUM && jc == CB;
-    const int j = is_norm_col ? dv : c0 + jc;             // column of the state
-    const bool live = is_norm_col ? part < LANES : (jc < CB && j < dv);
+    const bool is_norm_col = MODE == MODE_GATED_SUM && jc == GROUPS;     // its first column is the normaliser's
+    int j[CPT];                                           // columns of the state
+    bool live[CPT];
+#pragma unroll
+    for (int cc = 0; cc < CPT; ++cc) {
+        j[cc] = is_norm_col ? dv : c0 + jc * CPT + cc;
+        live[cc] = is_norm_col ? cc == 0 : (jc < GROUPS && j[cc] < dv);
+    }
     const int t0 = p.cu_q[req], t1 = p.cu_q[req + 1];
     if (t0 >= t1) return;
     const int kvh = head / (p.heads / p.kv_heads);
     float* slot = p.state + (size_t)p.slots[req] * p.state_stride;
     float* s_head = slot + (size_t)head * dk * cols;
     float* m_state = slot + (size_t)p.heads * dk * cols + head;
-    const bool fused = gridDim.z == 1;
+    const bool fused = !p.cut;
     const float q_scale = rsqrtf((float)dk);
+    const int row0 = part * (4 * VPT);                    // register ii holds row 64 (ii / (4 VPT)) + row0 + ii % (4 VPT)
 
-    // lane `part` of a column holds rows 16 g + 4 part + x (x = 0..3): the lanes of a column read
-    // neighbouring 16-byte pieces of a token's k and q
-    float S[NI];
+    float S[CPT][NI];
 #pragma unroll
     for (int ii = 0; ii < NI; ++ii) {
-        const int i = (ii / 4) * (4 * LANES) + part * 4 + ii % 4;
-        S[ii] = (live && i < dk) ? s_head[(size_t)i * cols + j] : 0.0f;
+        const int i = (ii / (4 * VPT)) * 64 + row0 + ii % (4 * VPT);
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) S[cc][ii] = (live[cc] && i < dk) ? s_head[(size_t)i * cols + j[cc]] : 0.0f;
     }
     if (MODE == MODE_GATED_SUM && tid == 0) m_carry = *m_state;
 
-    for (int tile0 = t0; tile0 < t1; tile0 += TT) {
+    // a tile's k, q, v and per-token scalars on their way into buffer `buf` (zeros outside the tile and the head)
+    auto stage = [&](int buf, int tile0) {
         const int nt = min(TT, t1 - tile0);
-        __syncthreads();                                  // the tile before is written out
-        for (int e = tid; e < TT * DMAX; e += THREADS) {
-            const int tt = e / DMAX, c = e % DMAX;
-            const bool ok = tt < nt && c < dk;
-            ks[tt][c] = ok ? p.k[(size_t)(tile0 + tt) * p.k_stride + kvh * dk + c] : 0.0f;
-            qs[tt][c] = ok ? p.q[(size_t)(tile0 + tt) * p.q_stride + kvh * dk + c] : 0.0f;
+        const float* kp = p.k + (size_t)kvh * dk;
+        const float* qp = p.q + (size_t)kvh * dk;
+        const float* vp = p.v + (size_t)head * dv + c0;
+        if (p.vec4) {
+            for (int e = tid; e < TT * (DMAX / 4); e += THREADS) {
+                const int tt = e / (DMAX / 4), c = (e % (DMAX / 4)) * 4;
+                const bool ok = tt < nt && c < dk;
+                const size_t t = ok ? tile0 + tt : t0;
+                cp_async16(&ks_[buf][tt][c], kp + t * p.k_stride + (ok ? c : 0), ok);
+                cp_async16(&qs_[buf][tt][c], qp + t * p.q_stride + (ok ? c : 0), ok);
+            }
+            for (int e = tid; e < TT * (CB / 4); e += THREADS) {
+                const int tt = e / (CB / 4), c = (e % (CB / 4)) * 4;
+                const bool ok = tt < nt && c0 + c < dv;
+                cp_async16(&vs_[buf][tt][c], vp + (size_t)(ok ? tile0 + tt : t0) * p.v_stride + (ok ? c : 0), ok);
+            }
+        } else {
+            for (int e = tid; e < TT * DMAX; e += THREADS) {
+                const int tt = e / DMAX, c = e % DMAX;
+                const bool ok = tt < nt && c < dk;
+                const size_t t = ok ? tile0 + tt : t0;
+                cp_async4(&ks_[buf][tt][c], kp + t * p.k_stride + (ok ? c : 0), ok);
+                cp_async4(&qs_[buf][tt][c], qp + t * p.q_stride + (ok ? c : 0), ok);
+            }
+            for (int e = tid; e < TT * CB; e += THREADS) {
+                const int tt = e / CB, c = e % CB;
+                const bool ok = tt < nt && c0 + c < dv;
+                cp_async4(&vs_[buf][tt][c], vp + (size_t)(ok ? tile0 + tt : t0) * p.v_stride + (ok ? c : 0), ok);
+            }
         }
-        for (int e = tid; e < TT * CS; e += THREADS) {
-            const int tt = e / CS, c = e % CS;
-            float x = 0.0f;
-            if (c == CB) x = 1.0f;
-            else if (tt < nt && c0 + c < dv) x = p.v[(size_t)(tile0 + tt) * p.v_stride + head * dv + c0 + c];
-            vs[tt][c] = x;
+        if (tid < TT) {
+            const bool ok = tid < nt;
+            const size_t t = ok ? tile0 + tid : t0;
+            cp_async4(&s0s[buf][tid], p.s0 + t * p.s0_stride + head, ok);
+            cp_async4(&s1s[buf][tid], p.s1 + t * p.s1_stride + head, ok);
         }
-        __syncthreads();
-        // ---- per-token scalars -----------------------------------------------------------------
+        cp_async_commit();
+    };
+    stage(0, t0);
+
+    int buf = 0;
+    for (int tile0 = t0; tile0 < t1; tile0 += TT, buf ^= 1) {
+        const int nt = min(TT, t1 - tile0);
+        float (*ks)[DMAX] = ks_[buf], (*qs)[DMAX] = qs_[buf];
+        float (*vs)[CB] = vs_[buf];
+        const float* s0t = s0s[buf];
+        const float* s1t = s1s[buf];
+        cp_async_wait_all();
+        __syncthreads();                                  // this tile is in; the tile before is written out
+        if (tile0 + TT < t1) stage(buf ^ 1, tile0 + TT);  // the next tile travels while this one is worked
+        // ---- per-token scalars; past the portion's end a token that changes nothing (decay 1, write 0) ----
         if (MODE == MODE_DELTA) {
-            for (int tt = tid / 32; tt < nt; tt += THREADS / 32) {
-                const int lane = tid % 32;
+            if (tid < 8 * TT) {                           // eight lanes a token: the unit norms of q and k
+                const int tt = tid / 8, l = tid % 8;
                 float sq = 0.0f, sk = 0.0f;
-                for (int c = lane; c < dk; c += 32) {
+                for (int c = l; c < DMAX; c += 8) {
                     sq = fmaf(qs[tt][c], qs[tt][c], sq);
                     sk = fmaf(ks[tt][c], ks[tt][c], sk);
                 }
-                sq = warp_sum(sq);
-                sk = warp_sum(sk);
-                const float fq = q_scale / sqrtf(sq + 1e-6f), fk = 1.0f / sqrtf(sk + 1e-6f);
-                for (int c = lane; c < dk; c += 32) { qs[tt][c] *= fq; ks[tt][c] *= fk; }
-                if (lane == 0) {
-                    const size_t t = tile0 + tt;
-                    const float b = p.s0[t * p.s0_stride + head], a = p.s1[t * p.s1_stride + head];
-                    sb[tt] = 1.0f / (1.0f + expf(-b));
-                    sa[tt] = expf(-expf(p.c0[head]) * softplusf_(a + p.c1[head]));
+#pragma unroll
+                for (int sh = 1; sh < 8; sh *= 2) {
+                    sq += __shfl_xor_sync(0xffffffffu, sq, sh);
+                    sk += __shfl_xor_sync(0xffffffffu, sk, sh);
+                }
+                if (l == 0) {
+                    const bool in = tt < nt;
+                    sfq[tt] = in ? q_scale / sqrtf(sq + 1e-6f) : 0.0f;
+                    sfk[tt] = in ? 1.0f / sqrtf(sk + 1e-6f) : 0.0f;
+                    sb[tt] = in ? 1.0f / (1.0f + expf(-s0t[tt])) : 0.0f;
+                    sa[tt] = in ? expf(-expf(p.c0[head]) * softplusf_(s1t[tt] + p.c1[head])) : 1.0f;
                 }
             }
         } else {
@@ -144,108 +237,136 @@ matrix_state_kernel(const MatrixStateArgs p) {
                 const int tt = tid;
                 float gi = 0.0f, gf = 0.0f;
                 if (tt < nt) {
-                    const size_t t = tile0 + tt;
-                    gi = p.cap * tanhf((p.s0[t * p.s0_stride + head] + p.c0[head]) / p.cap);
-                    gf = logsigmoidf_(p.cap * tanhf((p.s1[t * p.s1_stride + head] + p.c1[head]) / p.cap));
-                    sa[tt] = gf;
-                    sb[tt] = gi;
+                    gi = p.cap * tanhf((s0t[tt] + p.c0[head]) / p.cap);
+                    gf = logsigmoidf_(p.cap * tanhf((s1t[tt] + p.c1[head]) / p.cap));
                 }
-                __syncwarp();
-                if (tid == 0) {                           // the running maximum, in order
-                    float m = m_carry;
-                    for (int x = 0; x < nt; ++x) {
-                        const float mn = fmaxf(sa[x] + m, sb[x]);
-                        inv_s[x] = m;                     // the maximum before this token
-                        sm[x] = mn;
+                // the running maximum, in order: every lane walks the tile's gates in registers and keeps its own token's
+                float m = m_carry, m_before = 0.0f, m_mine = 0.0f;
+#pragma unroll
+                for (int x = 0; x < TT; ++x) {
+                    const float fx = __shfl_sync(0xffffffffu, gf, x), ix = __shfl_sync(0xffffffffu, gi, x);
+                    if (x < nt) {
+                        const float mn = fmaxf(fx + m, ix);
+                        if (x == tt) { m_before = m; m_mine = mn; }
                         m = mn;
                     }
-                    m_carry = m;
                 }
                 __syncwarp();
-                if (tt < nt) {
-                    sa[tt] = expf(gf + inv_s[tt] - sm[tt]);
-                    sb[tt] = expf(gi - sm[tt]);
+                if (tid == 0) m_carry = m;
+                if (tt < TT) {
+                    sm[tt] = tt < nt ? expf(-m_mine) : 1.0f;                    // what the normaliser is held against
+                    sa[tt] = tt < nt ? expf(gf + m_before - m_mine) : 1.0f;
+                    sb[tt] = tt < nt ? expf(gi - m_mine) : 0.0f;
                 }
-            }
-            __syncthreads();
-            for (int e = tid; e < nt * DMAX; e += THREADS) {
-                const int tt = e / DMAX, c = e % DMAX;
-                ks[tt][c] *= sb[tt];                      // the input gate rides on the key
-                qs[tt][c] *= q_scale;
             }
         }
         __syncthreads();
         // ---- the recurrence: the tile's tokens one after another, no barrier between them -------
-        float o_part[TT];
+        float o_part[TT][CPT];
+        auto token = [&](const int tt) {
+            const float* krow = &ks[tt][row0];
+            const float* qrow = &qs[tt][row0];
+            const float dec = sa[tt];
+            float vj[CPT], acc[CPT][VPT][4], w[VPT];
 #pragma unroll
-        for (int tt = 0; tt < TT; ++tt) {
-            o_part[tt] = 0.0f;
-            if (tt < nt) {
-                const float vj = vs[tt][is_norm_col ? CB : (jc < CB ? jc : 0)];
-                const float4* k4 = reinterpret_cast<const float4*>(&ks[tt][part * 4]);
-                const float4* q4 = reinterpret_cast<const float4*>(&qs[tt][part * 4]);
-                const float dec = sa[tt];
-                if (MODE == MODE_DELTA) {
-                    float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
+            for (int cc = 0; cc < CPT; ++cc) vj[cc] = is_norm_col ? 1.0f : vs[tt][jc < GROUPS ? jc * CPT + cc : 0];
+            if (MODE == MODE_DELTA) {
+                const float fk = sfk[tt];
 #pragma unroll
-                    for (int g4 = 0; g4 < NI / 4; ++g4) {
-                        const float4 kq = k4[g4 * LANES];
-                        d0 = fmaf(S[g4 * 4 + 0], kq.x, d0);
-                        d1 = fmaf(S[g4 * 4 + 1], kq.y, d1);
-                        d2 = fmaf(S[g4 * 4 + 2], kq.z, d2);
-                        d3 = fmaf(S[g4 * 4 + 3], kq.w, d3);
+                for (int cc = 0; cc < CPT; ++cc)
+#pragma unroll
+                    for (int v = 0; v < VPT; ++v) acc[cc][v][0] = acc[cc][v][1] = acc[cc][v][2] = acc[cc][v][3] = 0.0f;
+#pragma unroll
+                for (int g = 0; g < NG; ++g) {
+#pragma unroll
+                    for (int v = 0; v < VPT; ++v) {
+                        const float4 kq = *reinterpret_cast<const float4*>(krow + g * 64 + v * 4);
+                        const int at = (g * VPT + v) * 4;
+#pragma unroll
+                        for (int cc = 0; cc < CPT; ++cc) {
+                            acc[cc][v][0] = fmaf(S[cc][at + 0], kq.x, acc[cc][v][0]);
+                            acc[cc][v][1] = fmaf(S[cc][at + 1], kq.y, acc[cc][v][1]);
+                            acc[cc][v][2] = fmaf(S[cc][at + 2], kq.z, acc[cc][v][2]);
+                            acc[cc][v][3] = fmaf(S[cc][at + 3], kq.w, acc[cc][v][3]);
+                        }
                     }
-                    float dot = (d0 + d1) + (d2 + d3);
-                    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-                    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-                    const float u = sb[tt] * (vj - dec * dot);
-                    float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
-#pragma unroll
-                    for (int g4 = 0; g4 < NI / 4; ++g4) {
-                        const float4 kq = k4[g4 * LANES], qq = q4[g4 * LANES];
-                        S[g4 * 4 + 0] = fmaf(dec, S[g4 * 4 + 0], kq.x * u);
-                        S[g4 * 4 + 1] = fmaf(dec, S[g4 * 4 + 1], kq.y * u);
-                        S[g4 * 4 + 2] = fmaf(dec, S[g4 * 4 + 2], kq.z * u);
-                        S[g4 * 4 + 3] = fmaf(dec, S[g4 * 4 + 3], kq.w * u);
-                        o0 = fmaf(S[g4 * 4 + 0], qq.x, o0);
-                        o1 = fmaf(S[g4 * 4 + 1], qq.y, o1);
-                        o2 = fmaf(S[g4 * 4 + 2], qq.z, o2);
-                        o3 = fmaf(S[g4 * 4 + 3], qq.w, o3);
-                    }
-                    o_part[tt] = (o0 + o1) + (o2 + o3);
-                } else {
-                    float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
-#pragma unroll
-                    for (int g4 = 0; g4 < NI / 4; ++g4) {
-                        const float4 kq = k4[g4 * LANES], qq = q4[g4 * LANES];
-                        S[g4 * 4 + 0] = fmaf(dec, S[g4 * 4 + 0], kq.x * vj);
-                        S[g4 * 4 + 1] = fmaf(dec, S[g4 * 4 + 1], kq.y * vj);
-                        S[g4 * 4 + 2] = fmaf(dec, S[g4 * 4 + 2], kq.z * vj);
-                        S[g4 * 4 + 3] = fmaf(dec, S[g4 * 4 + 3], kq.w * vj);
-                        o0 = fmaf(S[g4 * 4 + 0], qq.x, o0);
-                        o1 = fmaf(S[g4 * 4 + 1], qq.y, o1);
-                        o2 = fmaf(S[g4 * 4 + 2], qq.z, o2);
-                        o3 = fmaf(S[g4 * 4 + 3], qq.w, o3);
-                    }
-                    o_part[tt] = (o0 + o1) + (o2 + o3);
                 }
+#pragma unroll
+                for (int cc = 0; cc < CPT; ++cc) {
+#pragma unroll
+                    for (int v = 0; v < VPT; ++v)
+                        w[v] = (acc[cc][v][0] + acc[cc][v][1]) + (acc[cc][v][2] + acc[cc][v][3]);
+                    const float dot = fk * lanes_sum<VPT, LANES>(w);          // S^T k of the unit key
+                    vj[cc] = fk * (sb[tt] * (vj[cc] - dec * dot));             // u, with the key's unit norm
+                }
+            } else {
+#pragma unroll
+                for (int cc = 0; cc < CPT; ++cc) vj[cc] *= sb[tt];             // the input gate
+            }
+#pragma unroll
+            for (int cc = 0; cc < CPT; ++cc)
+#pragma unroll
+                for (int v = 0; v < VPT; ++v) acc[cc][v][0] = acc[cc][v][1] = acc[cc][v][2] = acc[cc][v][3] = 0.0f;
+#pragma unroll
+            for (int g = 0; g < NG; ++g) {
+#pragma unroll
+                for (int v = 0; v < VPT; ++v) {
+                    const float4 kq = *reinterpret_cast<const float4*>(krow + g * 64 + v * 4);
+                    const float4 qq = *reinterpret_cast<const float4*>(qrow + g * 64 + v * 4);
+                    const int at = (g * VPT + v) * 4;
+#pragma unroll
+                    for (int cc = 0; cc < CPT; ++cc) {
+                        S[cc][at + 0] = fmaf(dec, S[cc][at + 0], kq.x * vj[cc]);
+                        S[cc][at + 1] = fmaf(dec, S[cc][at + 1], kq.y * vj[cc]);
+                        S[cc][at + 2] = fmaf(dec, S[cc][at + 2], kq.z * vj[cc]);
+                        S[cc][at + 3] = fmaf(dec, S[cc][at + 3], kq.w * vj[cc]);
+                        acc[cc][v][0] = fmaf(S[cc][at + 0], qq.x, acc[cc][v][0]);
+                        acc[cc][v][1] = fmaf(S[cc][at + 1], qq.y, acc[cc][v][1]);
+                        acc[cc][v][2] = fmaf(S[cc][at + 2], qq.z, acc[cc][v][2]);
+                        acc[cc][v][3] = fmaf(S[cc][at + 3], qq.w, acc[cc][v][3]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int cc = 0; cc < CPT; ++cc) {
+#pragma unroll
+                for (int v = 0; v < VPT; ++v) w[v] = (acc[cc][v][0] + acc[cc][v][1]) + (acc[cc][v][2] + acc[cc][v][3]);
+                o_part[tt][cc] = VPT == 4 ? (w[0] + w[VPT > 1 ? 1 : 0]) + (w[VPT > 2 ? 2 : 0] + w[VPT > 3 ? 3 : 0]) : w[0];
+            }
+        };
+        if (nt == TT) {
+#pragma unroll
+            for (int tt = 0; tt < TT; ++tt) token(tt);
+        } else {
+#pragma unroll
+            for (int tt = 0; tt < TT; ++tt) {
+#pragma unroll
+                for (int cc = 0; cc < CPT; ++cc) o_part[tt][cc] = 0.0f;
+                if (tt < nt) token(tt);
             }
         }
 #pragma unroll
-        for (int sh = 1; sh < LANES; sh *= 2) {
-#pragma unroll
-            for (int tt = 0; tt < TT; ++tt) o_part[tt] += __shfl_xor_sync(0xffffffffu, o_part[tt], sh);
-        }
-        if (part == 0 && (jc < CB || is_norm_col)) {
+        for (int sh = 1; sh < LANES; sh *= 2) {           // the threads of a column, all tokens of the tile at once
 #pragma unroll
             for (int tt = 0; tt < TT; ++tt)
-                if (tt < nt) os[tt][is_norm_col ? CB : jc] = live ? o_part[tt] : 0.0f;
+#pragma unroll
+                for (int cc = 0; cc < CPT; ++cc) o_part[tt][cc] += __shfl_xor_sync(0xffffffffu, o_part[tt][cc], sh);
+        }
+        if (part == 0 && (jc < GROUPS || is_norm_col)) {
+#pragma unroll
+            for (int tt = 0; tt < TT; ++tt) {
+                const float scale = MODE == MODE_DELTA ? sfq[tt] : q_scale;
+#pragma unroll
+                for (int cc = 0; cc < CPT; ++cc)
+                    if (tt < nt && (!is_norm_col || cc == 0))
+                        os[tt][is_norm_col ? CB : jc * CPT + cc] = live[cc] ? o_part[tt][cc] * scale : 0.0f;
+            }
         }
         __syncthreads();
         if (MODE == MODE_GATED_SUM) {                     // the normaliser: n . q against e^-m
             for (int e = tid; e < nt * CB; e += THREADS) {
                 const int tt = e / CB, c = e % CB;
-                const float den = fmaxf(fabsf(os[tt][CB]), expf(-sm[tt])) + 1e-6f;
+                const float den = fmaxf(fabsf(os[tt][CB]), sm[tt]) + 1e-6f;
                 os[tt][c] = os[tt][c] / den;
             }
             __syncthreads();
@@ -278,13 +399,16 @@ matrix_state_kernel(const MatrixStateArgs p) {
     }
     __syncthreads();
     float* carry = fused ? nullptr : p.carry + ((size_t)req * p.heads + head) * (dk + 1);
-    if (live && (!is_norm_col || blockIdx.z == 0)) {
 #pragma unroll
-        for (int ii = 0; ii < NI; ++ii) {
-            const int i = (ii / 4) * (4 * LANES) + part * 4 + ii % 4;
-            if (i < dk) {
-                if (is_norm_col && !fused) carry[i] = S[ii];
-                else s_head[(size_t)i * cols + j] = S[ii];
+    for (int cc = 0; cc < CPT; ++cc) {
+        if (live[cc] && (!is_norm_col || blockIdx.z == 0)) {
+#pragma unroll
+            for (int ii = 0; ii < NI; ++ii) {
+                const int i = (ii / (4 * VPT)) * 64 + row0 + ii % (4 * VPT);
+                if (i < dk) {
+                    if (is_norm_col && !fused) carry[i] = S[cc][ii];
+                    else s_head[(size_t)i * cols + j[cc]] = S[cc][ii];
+                }
             }
         }
     }
@@ -333,16 +457,20 @@ matrix_state_finish_kernel(const float* o_raw, const float* __restrict__ norm_we
 template <int MODE, int DMAX>
 int launch_cb(const MatrixStateArgs& a, int requests, int cb, int col_blocks, cudaStream_t s) {
     dim3 grid(requests, a.heads, col_blocks);
-    const int extra = MODE == MODE_GATED_SUM ? 32 : 0;
-    if (cb == 32) matrix_state_kernel<MODE, DMAX, 32><<<grid, LANES * 32 + extra, 0, s>>>(a);
-    else if (cb == 64) matrix_state_kernel<MODE, DMAX, 64><<<grid, LANES * 64 + extra, 0, s>>>(a);
-    else matrix_state_kernel<MODE, DMAX, 128><<<grid, LANES * 128 + extra, 0, s>>>(a);
+#define TI_MS_GO(CB_, LANES_) \
+    matrix_state_kernel<MODE, DMAX, CB_, LANES_><<<grid, StateBlock<MODE, CB_, LANES_>::threads, 0, s>>>(a)
+    if (a.cut && cb == 8) TI_MS_GO(8, 16);
+    else if (a.cut && cb == 16) TI_MS_GO(16, 16);
+    else if (a.cut && cb == 32) TI_MS_GO(32, 16);
+    else if (cb == 32) TI_MS_GO(32, 4);
+    else if (cb == 64) TI_MS_GO(64, 4);
+    else TI_MS_GO(128, 4);
+#undef TI_MS_GO
     return 0;
 }
 
 template <int MODE>
 int launch_dk(const MatrixStateArgs& a, int requests, int cb, int col_blocks, cudaStream_t s) {
-    if (a.dk <= 32) return launch_cb<MODE, 32>(a, requests, cb, col_blocks, s);
     if (a.dk <= 64) return launch_cb<MODE, 64>(a, requests, cb, col_blocks, s);
     if (a.dk <= 128) return launch_cb<MODE, 128>(a, requests, cb, col_blocks, s);
     return launch_cb<MODE, 256>(a, requests, cb, col_blocks, s);
@@ -357,7 +485,8 @@ extern "C" long long ti_matrix_state_floats(int mode, int heads, int dk, int dv)
 }
 
 // col_block: 0 = a head's columns in one block (dv <= 128) with the norm, weight and gate in the same launch;
-// 32, 64 or 128 = that many columns a block, o left in `o_raw` and finished by a second launch.
+// 8, 16, 32, 64 or 128 = that many columns a block (16 threads a column up to 32 columns, 4 beyond), o left in
+// `o_raw` and finished by a second launch.
 extern "C" int ti_matrix_state(int mode, const float* q, const float* k, const float* v, int q_stride, int k_stride,
                                int v_stride, const float* s0, int s0_stride, const float* s1, int s1_stride,
                                const float* c0, const float* c1, float cap, const float* gate, int gate_stride,
@@ -372,7 +501,7 @@ extern "C" int ti_matrix_state(int mode, const float* q, const float* k, const f
     TI_REQUIRE(heads >= 1 && kv_heads >= 1 && heads % kv_heads == 0, "matrix_state: %d heads over %d key heads",
                heads, kv_heads);
     TI_REQUIRE(out_dtype == TI_F32 || out_dtype == TI_BF16, "matrix_state: output dtype code %d", out_dtype);
-    TI_REQUIRE(col_block == 0 || col_block == 32 || col_block == 64 || col_block == 128,
+    TI_REQUIRE(col_block == 0 || col_block == 8 || col_block == 16 || col_block == 32 || col_block == 64 || col_block == 128,
                "matrix_state: %d columns a block", col_block);
     TI_REQUIRE(col_block != 0 || dv <= 128, "matrix_state: %d value columns do not fit one block", dv);
     TI_REQUIRE(col_block == 0 || o_raw != nullptr, "matrix_state: cut columns need the float32 rows");
@@ -386,6 +515,9 @@ extern "C" int ti_matrix_state(int mode, const float* q, const float* k, const f
     a.cu_q = cu_q; a.slots = slots; a.state = state; a.state_stride = state_stride;
     a.heads = heads; a.kv_heads = kv_heads; a.dk = dk; a.dv = dv;
     a.out = out; a.out_bf16 = out_dtype == TI_BF16; a.o_raw = o_raw; a.carry = carry;
+    a.cut = col_block != 0;
+    a.vec4 = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) % 16 == 0 &&
+              q_stride % 4 == 0 && k_stride % 4 == 0 && v_stride % 4 == 0 && dk % 4 == 0 && dv % 4 == 0) ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
     int cb = col_block, col_blocks = 1;
     if (cb == 0) cb = dv <= 32 ? 32 : dv <= 64 ? 64 : 128;

@@ -192,9 +192,9 @@ class StateOps:
         # few (request, head) pairs with long portions: a head's columns over several blocks
         col_block, o_raw, carry = 0, None, None
         pairs = step.num_requests * heads
-        if dv > 128 or (self.cut_state_columns and dv >= 64 and step.max_q_len > 64 and 2 * pairs <= self.num_sms):
-            col_block = 32
-            while col_block < 128 and pairs * -(-dv // col_block) > 2 * self.num_sms:
+        if dv > 128 or (self.cut_state_columns and dv >= 16 and step.max_q_len > 64 and pairs <= 2 * self.num_sms):
+            col_block = 8
+            while col_block < 128 and pairs * -(-dv // col_block) > 4 * self.num_sms:
                 col_block *= 2
             o_raw = torch.empty((t, heads * dv), dtype=torch.float32, device=q.device)
             self.launches += 1
