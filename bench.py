@@ -474,7 +474,7 @@ def timed_ops(engine, names, run, torch):
         setattr(ops, n, wrap(n, originals[n]))
     try:
         torch.cuda.synchronize()
-        torch.cuda._sleep(3_000_000)                 # about 2 ms: the launches queue up behind it
+        torch.cuda._sleep(12_000_000)                # about 6 ms: the launches of a whole step queue up behind it
         run()
         torch.cuda.synchronize()
     finally:
