@@ -211,7 +211,7 @@ def test_clamped_feed_forward(ops, sizes, dtype):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("sizes", [(5, 2, 24, 16), (4, 4, 8, None), (1, 1, 24, 8), (3, 1, 16, None), (16, 3, 32, None),
                                    (8, 2, 64, 128), (12, 5, 16, 16), (40, 6, 16, None)])
-@pytest.mark.parametrize("t", [1, 7, 150])
+@pytest.mark.parametrize("t", [1, 7, 150, 700])      # 700 rows: from 1,024 (row, expert) pairs the grouped tensor-core products
 def test_softmax_router_and_experts(ops, sizes, t, dtype):
     """The chosen experts' shares of the softmax over all experts weigh their outputs as they are
     (they do not sum to one); a shared expert with a limit of its own is added for every row."""

@@ -23,6 +23,7 @@
 // and a second launch adds the slabs in ascending order of K into C.  Every wait on an mbarrier
 // is bounded: on a timeout the block records status 2, frees its tensor memory and returns.
 #include "qkv_epilogue.cuh"
+#include "glu.cuh"
 
 namespace {
 
@@ -55,7 +56,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const __grid_constant__ qkv::Epilogue qkv_e, float* __restrict__ c,
                     bf16* __restrict__ out_act, int m, int n, int k, int ldc, int ld_act, int mode,
                     float* __restrict__ ws, int splits, int* __restrict__ status,
-                    const int* __restrict__ group_of_tile, const int* __restrict__ tiles_m_dev) {
+                    const int* __restrict__ group_of_tile, const int* __restrict__ tiles_m_dev,
+                    const GluArgs glu) {
     using T = Tile<BN>;
     constexpr int STAGES = T::STAGES;
     extern __shared__ unsigned char smem_raw[];
@@ -233,7 +235,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         for (int i = 0; i < 4; ++i) {
                             const float g0 = v[half * 16 + 2 * i], g1 = v[half * 16 + 2 * i + 1];
                             const float u0 = v[half * 16 + 8 + 2 * i], u1 = v[half * 16 + 9 + 2 * i];
-                            __nv_bfloat162 y = __floats2bfloat162_rn(silu_mul(g0, u0), silu_mul(g1, u1));
+                            __nv_bfloat162 y = glu.kind == GLU_SILU
+                                ? __floats2bfloat162_rn(silu_mul(g0, u0), silu_mul(g1, u1))
+                                : __floats2bfloat162_rn(glu_activation(glu.kind, g0, u0, glu.limit, glu.alpha),
+                                                        glu_activation(glu.kind, g1, u1, glu.limit, glu.alpha));
                             packed[i] = *reinterpret_cast<unsigned*>(&y);
                         }
                         *reinterpret_cast<uint4*>(out_act + (size_t)row * ld_act + (col + half * 16) / 2) =
@@ -350,7 +355,7 @@ int choose_splits(int m, int n, int k, int mode, int sms) {
 // width: the tiles' columns, 256, 128 or 64
 int launch_tiles(const void* a, const void* w, const qkv::Epilogue& e, float* c, void* out_act, int m, int n,
                  int k, int lda, int ldw, int ldc, int ld_act, int mode, int width, float* ws, int splits,
-                 int* status, void* stream, bool add_runs = true) {
+                 int* status, void* stream, bool add_runs = true, GluArgs glu = GluArgs{GLU_SILU, 0.0f, 0.0f}) {
     int device = 0, sms = 0;
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
@@ -375,17 +380,17 @@ int launch_tiles(const void* a, const void* w, const qkv::Epilogue& e, float* c,
         const int tiles = tiles_m * ((n + 255) / 256) * splits;
         ti_launch_pdl(gemm_tcgen05_kernel<256>, tiles < sms ? tiles : sms, THREADS, Tile<256>::SMEM,
                       (cudaStream_t)stream, map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, ws,
-                      splits, status, (const int*)nullptr, (const int*)nullptr);
+                      splits, status, (const int*)nullptr, (const int*)nullptr, glu);
     } else if (width == 128) {
         const int tiles = tiles_m * ((n + 127) / 128) * splits;
         ti_launch_pdl(gemm_tcgen05_kernel<128>, tiles < sms ? tiles : sms, THREADS, Tile<128>::SMEM,
                       (cudaStream_t)stream, map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, ws,
-                      splits, status, (const int*)nullptr, (const int*)nullptr);
+                      splits, status, (const int*)nullptr, (const int*)nullptr, glu);
     } else {
         const int tiles = tiles_m * ((n + 63) / 64) * splits;
         ti_launch_pdl(gemm_tcgen05_kernel<64>, tiles < sms ? tiles : sms, THREADS, Tile<64>::SMEM,
                       (cudaStream_t)stream, map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, ws,
-                      splits, status, (const int*)nullptr, (const int*)nullptr);
+                      splits, status, (const int*)nullptr, (const int*)nullptr, glu);
     }
     if (int rc = ti_check_launch("gemm_tcgen05")) return rc;
     if (splits > 1 && add_runs) {
@@ -462,10 +467,10 @@ extern "C" int ti_gemm_tcgen05(const void* a, const void* w, float* c, void* out
 // Grouped product: row tile i (128 rows of a) is multiplied by the i-th named group's weights,
 // w + group_of_tile[i] * n * ldw; `tiles_m_dev` (device) says how many row tiles there are, at most
 // m_max / 128.  c (MODE_STORE) or out_act (MODE_SWIGLU) has m_max rows.  Not a dependent launch.
-extern "C" int ti_gemm_tcgen05_grouped(const void* a, const void* w, float* c, void* out_act, int m_max, int n,
-                                       int k, int lda, int ldw, int ldc, int ld_act, int mode, int groups,
-                                       const int* group_of_tile, const int* tiles_m_dev, int* status,
-                                       void* stream) {
+static int gemm_tcgen05_grouped_impl(const void* a, const void* w, float* c, void* out_act, int m_max, int n,
+                                     int k, int lda, int ldw, int ldc, int ld_act, int mode, int groups,
+                                     const int* group_of_tile, const int* tiles_m_dev, int* status,
+                                     void* stream, GluArgs glu) {
     if (m_max == 0 || n == 0) return 0;
     TI_REQUIRE(mode == MODE_STORE || mode == MODE_SWIGLU, "gemm_tcgen05_grouped: mode %d", mode);
     TI_REQUIRE(m_max % BM == 0 && ti_gemm_tcgen05_supported(m_max, n, k, lda, ldw, ldc, mode),
@@ -498,12 +503,52 @@ extern "C" int ti_gemm_tcgen05_grouped(const void* a, const void* w, float* c, v
     if (width == 256)
         gemm_tcgen05_kernel<256><<<grid, THREADS, Tile<256>::SMEM, (cudaStream_t)stream>>>(
             map_a, map_w, qkv::Epilogue{}, c, (bf16*)out_act, m_max, n, k, ldc, ld_act, mode, nullptr, 1, status,
-            group_of_tile, tiles_m_dev);
+            group_of_tile, tiles_m_dev, glu);
     else
         gemm_tcgen05_kernel<128><<<grid, THREADS, Tile<128>::SMEM, (cudaStream_t)stream>>>(
             map_a, map_w, qkv::Epilogue{}, c, (bf16*)out_act, m_max, n, k, ldc, ld_act, mode, nullptr, 1, status,
-            group_of_tile, tiles_m_dev);
+            group_of_tile, tiles_m_dev, glu);
     return ti_check_launch("gemm_tcgen05_grouped");
+}
+
+extern "C" int ti_gemm_tcgen05_grouped(const void* a, const void* w, float* c, void* out_act, int m_max, int n,
+                                       int k, int lda, int ldw, int ldc, int ld_act, int mode, int groups,
+                                       const int* group_of_tile, const int* tiles_m_dev, int* status,
+                                       void* stream) {
+    return gemm_tcgen05_grouped_impl(a, w, c, out_act, m_max, n, k, lda, ldw, ldc, ld_act, mode, groups,
+                                     group_of_tile, tiles_m_dev, status, stream, GluArgs{GLU_SILU, 0.0f, 0.0f});
+}
+
+// The grouped product whose epilogue is the gated activation `glu_kind` of glu.cuh over groups of
+// 8 gate + 8 up columns: out_act[m_max, n/2].
+extern "C" int ti_gemm_tcgen05_grouped_glu(const void* a, const void* w, void* out_act, int m_max, int n, int k,
+                                           int lda, int ldw, int ld_act, int groups, const int* group_of_tile,
+                                           const int* tiles_m_dev, int glu_kind, float glu_limit, float glu_alpha,
+                                           int* status, void* stream) {
+    TI_REQUIRE(glu_kind == GLU_SILU || glu_kind == GLU_CLAMPED, "gemm_tcgen05_grouped_glu: activation %d", glu_kind);
+    return gemm_tcgen05_grouped_impl(a, w, nullptr, out_act, m_max, n, k, lda, ldw, 0, ld_act, MODE_SWIGLU, groups,
+                                     group_of_tile, tiles_m_dev, status, stream, GluArgs{glu_kind, glu_limit, glu_alpha});
+}
+
+// out_act[m, n/2] = act(gate, up) of a w^T over groups of 8 gate + 8 up columns, with the gated
+// activation `glu_kind` of glu.cuh in the epilogue (K uncut).
+extern "C" int ti_gemm_tcgen05_glu(const void* a, const void* w, void* out_act, int m, int n, int k, int lda,
+                                   int ldw, int ld_act, int glu_kind, float glu_limit, float glu_alpha, int* status,
+                                   void* stream) {
+    if (m == 0 || n == 0) return 0;
+    TI_REQUIRE(glu_kind == GLU_SILU || glu_kind == GLU_CLAMPED, "gemm_tcgen05_glu: activation %d", glu_kind);
+    TI_REQUIRE(ti_gemm_tcgen05_supported(m, n, k, lda, ldw, 0, MODE_SWIGLU),
+               "gemm_tcgen05_glu: K=%d and the row strides %d, %d must be multiples of 8, N=%d a multiple of 16", k, lda,
+               ldw, n);
+    TI_REQUIRE((uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out_act % 16 == 0 && ld_act % 8 == 0,
+               "gemm_tcgen05_glu: operands and output must be 16-byte aligned");
+    int device = 0, sms = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const int tiles_m = (m + BM - 1) / BM;
+    const int width = tiles_m * ((n + 255) / 256) >= sms ? 256 : tiles_m * ((n + 127) / 128) * 2 >= sms ? 128 : 64;
+    return launch_tiles(a, w, qkv::Epilogue{}, nullptr, out_act, m, n, k, lda, ldw, 0, ld_act, MODE_SWIGLU, width,
+                        nullptr, 1, status, stream, true, GluArgs{glu_kind, glu_limit, glu_alpha});
 }
 
 // The QKV product of a prompt portion with the epilogue of qkv_epilogue.cuh (head size 128), on

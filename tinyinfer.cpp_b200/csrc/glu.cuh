@@ -6,6 +6,9 @@
 
 enum { GLU_SILU = 0, GLU_CLAMPED = 1 };
 
+// What an epilogue needs to know of the activation; kind GLU_SILU ignores the rest.
+struct GluArgs { int kind; float limit, alpha; };
+
 __device__ __forceinline__ float glu_activation(int kind, float g, float u, float limit, float alpha) {
     if (kind == GLU_CLAMPED) {
         g = fminf(g, limit);

@@ -310,7 +310,7 @@ __global__ void moe_gather_scaled_kernel(const bf16* __restrict__ h, int h_strid
     const int row = blockIdx.x;
     if (row >= tiles_m[0] * 128) return;
     const int pair = row_pair[row];
-    const float w = pair >= 0 ? weights[pair] : 0.0f;
+    const float w = pair >= 0 ? (weights != nullptr ? weights[pair] : 1.0f) : 0.0f;     // no weights: the rows as they are
     const bf16* src = h + (size_t)(pair >= 0 ? pair / top : 0) * h_stride;
     for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -328,7 +328,8 @@ __global__ void moe_gather_scaled_kernel(const bf16* __restrict__ h, int h_strid
 }
 
 __global__ void moe_combine_rows_kernel(const float* __restrict__ rows, const int* __restrict__ pos_of_pair, int top,
-                                        int width, int num_tokens, float* __restrict__ residual, int res_stride) {
+                                        int width, int num_tokens, float* __restrict__ residual, int res_stride,
+                                        const float* __restrict__ weights) {
     const int quads = width >> 2;                      // width is a multiple of 8 on this path
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)num_tokens * quads) return;
@@ -336,7 +337,9 @@ __global__ void moe_combine_rows_kernel(const float* __restrict__ rows, const in
     float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     for (int s = 0; s < top; ++s) {
         const float4 v = *reinterpret_cast<const float4*>(rows + (size_t)pos_of_pair[t * top + s] * width + c);
-        total.x += v.x; total.y += v.y; total.z += v.z; total.w += v.w;
+        const float w = weights != nullptr ? weights[t * top + s] : 1.0f;            // a pair's weight on its expert's output
+        total.x = fmaf(w, v.x, total.x); total.y = fmaf(w, v.y, total.y);
+        total.z = fmaf(w, v.z, total.z); total.w = fmaf(w, v.w, total.w);
     }
     float* dst = residual + (size_t)t * res_stride + c;
     dst[0] += total.x; dst[1] += total.y; dst[2] += total.z; dst[3] += total.w;
@@ -364,12 +367,12 @@ extern "C" int ti_moe_gather_scaled(const void* h, int h_stride, const int* row_
 }
 
 extern "C" int ti_moe_combine_rows(const float* rows, const int* pos_of_pair, int top, int width, int num_tokens,
-                                   float* residual, int res_stride, void* stream) {
+                                   float* residual, int res_stride, const float* weights, void* stream) {
     TI_REQUIRE(width % 4 == 0 && ((uintptr_t)rows) % 16 == 0, "moe_combine_rows: rows of four-float groups, 16-byte aligned");
     const size_t total = (size_t)num_tokens * (width / 4);
     if (total == 0) return 0;
     moe_combine_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        rows, pos_of_pair, top, width, num_tokens, residual, res_stride);
+        rows, pos_of_pair, top, width, num_tokens, residual, res_stride, weights);
     return ti_check_launch("moe_combine_rows");
 }
 

@@ -250,6 +250,9 @@ class CudaOps(MixerOps, StateOps):
             b.ti_gemm_tcgen05_supported.argtypes = [_i, _i, _i, _i, _i, _i, _i]
             b.ti_gemm_tcgen05_grouped.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp,
                                                   _vp, _vp]
+            b.ti_gemm_tcgen05_grouped_glu.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _f, _f,
+                                                      _vp, _vp]
+            b.ti_gemm_tcgen05_glu.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _vp]
             b.ti_gemm_tcgen05_2sm.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]
             qkv_args = [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i,
                         _i, _i, _vp, _vp, _vp]
@@ -291,7 +294,7 @@ class CudaOps(MixerOps, StateOps):
                                          _vp, _vp, _i, _i, _f, _f, _vp]
             b.ti_moe_sort_padded.argtypes = [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]
             b.ti_moe_gather_scaled.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp]
-            b.ti_moe_combine_rows.argtypes = [_vp, _vp, _i, _i, _i, _vp, _i, _vp]
+            b.ti_moe_combine_rows.argtypes = [_vp, _vp, _i, _i, _i, _vp, _i, _vp, _vp]
             self._gated = b
         return self._gated
 
@@ -563,12 +566,23 @@ class CudaOps(MixerOps, StateOps):
         gated activation ``kind`` of ``glu_rows`` ("clamped": ``g = min(g, limit)``, ``u = clamp(u,
         -limit, limit)``, ``g sigmoid(alpha g) (u + 1)``); ``row_scale`` (float32, one per row)
         multiplies a row's activations."""
-        m = h.shape[0]
+        from .state_ops import GLU_KINDS
+        m, k = h.shape
         inter = w_down.shape[1]
-        gu = torch.empty((m, 2 * inter), dtype=torch.float32, device=h.device)
-        self.linear(h, w_gate_up, gu)
+        interleaved = bool(getattr(w_gate_up, "_ti_interleaved", False))
         y = torch.empty((m, inter), dtype=h.dtype, device=h.device)
-        self.glu_rows(gu, bool(getattr(w_gate_up, "_ti_interleaved", False)), kind, limit, alpha, y)
+        if (interleaved and m > 64 and h.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16
+                and inter % 8 == 0 and h.data_ptr() % 16 == 0 and self.bf16.ti_gemm_tcgen05_supported(
+                    m, 2 * inter, k, h.stride(0), w_gate_up.stride(0), 0, 2)):
+            # many rows: the activation in the epilogue of the tcgen05 product
+            self._ok(self.bf16.ti_gemm_tcgen05_glu(
+                h.data_ptr(), w_gate_up.data_ptr(), y.data_ptr(), m, 2 * inter, k, h.stride(0), w_gate_up.stride(0),
+                y.stride(0), GLU_KINDS[kind], float(limit), float(alpha), self.status.data_ptr(), self._stream()),
+                self.bf16)
+        else:
+            gu = torch.empty((m, 2 * inter), dtype=torch.float32, device=h.device)
+            self.linear(h, w_gate_up, gu)
+            self.glu_rows(gu, interleaved, kind, limit, alpha, y)
         if row_scale is not None:
             self.scale_rows(y, row_scale)
         self.linear(y, w_down, residual, accumulate=True)
@@ -1091,10 +1105,11 @@ class CudaOps(MixerOps, StateOps):
                 and self.gated.ti_moe_grouped_supported(width, ff, experts)):
             pairs = t * top
             if (self.tcgen05_experts_from is not None and pairs >= self.tcgen05_experts_from and interleaved
-                    and ff % 16 == 0 and width % 8 == 0 and act_kind == 0):
+                    and ff % 16 == 0 and width % 8 == 0):
                 # every expert's pairs in whole tiles of 128 rows, the rows of h times their weights
                 # gathered in that order, two grouped tcgen05 products (the first with SwiGLU in its
-                # epilogue), and the pairs' rows added per token
+                # epilogue), and the pairs' rows added per token; with another activation the rows of h
+                # are gathered as they are and the weights scale the pairs' rows as they are added
                 max_rows = (pairs // 128 + experts) * 128
                 ints = torch.empty(max_rows + pairs + max_rows // 128 + 1, dtype=torch.int32, device=h.device)
                 row_pair, pos_of_pair = ints[:max_rows], ints[max_rows:max_rows + pairs]
@@ -1105,20 +1120,21 @@ class CudaOps(MixerOps, StateOps):
                                               self._stream()), g)
                 a = torch.empty((max_rows, width), dtype=torch.bfloat16, device=h.device)
                 self._ok(g.ti_moe_gather_scaled(h.data_ptr(), h.stride(0), row_pair.data_ptr(), tiles_m.data_ptr(),
-                                                weights.data_ptr(), top, width, max_rows, a.data_ptr(),
-                                                self._stream()), g)
+                                                weights.data_ptr() if act_kind == 0 else None, top, width, max_rows,
+                                                a.data_ptr(), self._stream()), g)
                 y = torch.empty((max_rows, ff), dtype=torch.bfloat16, device=h.device)
-                self._ok(self.bf16.ti_gemm_tcgen05_grouped(
-                    a.data_ptr(), gate_up.data_ptr(), None, y.data_ptr(), max_rows, 2 * ff, width, width, width, 0,
-                    ff, 2, experts, group_of_tile.data_ptr(), tiles_m.data_ptr(), self.status.data_ptr(),
-                    self._stream()), self.bf16)
+                self._ok(self.bf16.ti_gemm_tcgen05_grouped_glu(
+                    a.data_ptr(), gate_up.data_ptr(), y.data_ptr(), max_rows, 2 * ff, width, width, width, ff,
+                    experts, group_of_tile.data_ptr(), tiles_m.data_ptr(), act_kind, act_limit, act_alpha,
+                    self.status.data_ptr(), self._stream()), self.bf16)
                 out_rows = torch.empty((max_rows, width), dtype=torch.float32, device=h.device)
                 self._ok(self.bf16.ti_gemm_tcgen05_grouped(
                     y.data_ptr(), w["down"].data_ptr(), out_rows.data_ptr(), None, max_rows, width, ff, ff, ff,
                     width, 0, 0, experts, group_of_tile.data_ptr(), tiles_m.data_ptr(), self.status.data_ptr(),
                     self._stream()), self.bf16)
                 self._ok(g.ti_moe_combine_rows(out_rows.data_ptr(), pos_of_pair.data_ptr(), top, width, t,
-                                               residual.data_ptr(), residual.stride(0), self._stream()), g)
+                                               residual.data_ptr(), residual.stride(0),
+                                               None if act_kind == 0 else weights.data_ptr(), self._stream()), g)
                 if shared is not None:
                     self._shared_expert(h, shared, residual)
                 return
