@@ -116,7 +116,7 @@ def test_norm_in_groups(ops, sizes, dtype):
     assert ((acc.cpu().double() - (res.double() + want)).abs() / (1 + want.abs())).max() < 1e-5
 
 
-@pytest.mark.parametrize("taps", [1, 2, 3, 4, 7])
+@pytest.mark.parametrize("taps", [1, 2, 3, 4, 7, 12])
 @pytest.mark.parametrize("options", [(False, False), (True, False), (False, True)])
 def test_time_convolution_over_portions(ops, taps, options):
     """Three requests in portions as short as one row, shorter than the taps reach; slots in another

@@ -22,7 +22,7 @@
 
 namespace {
 
-constexpr int MAX_TAPS = 8;
+constexpr int MAX_TAPS = 16;
 
 template <typename TO>
 __global__ void __launch_bounds__(256)
