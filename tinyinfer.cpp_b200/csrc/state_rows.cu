@@ -6,7 +6,8 @@
 //    taps - 1 inputs, zeros for a new request).  Options: add the input (x + conv(x)), silu on the
 //    result.  With taps = 0 it converts the rows.  `conv_tail_store` then renews the state; it runs
 //    as a launch of its own behind the convolution, so no block reads a state that another one
-//    has already overwritten.
+//    has already overwritten.  Where every request brings one token (`renew`), the one thread that
+//    reads a request's kept rows of a channel moves them up itself.
 //  * group_norm_rows: RMS norm in `groups` equal consecutive parts of a row, each divided by its
 //    own sqrt(mean(x^2) + eps), the whole times a weight per element; stored (optionally for
 //    gathered rows) or added to a float32 residual.
@@ -29,7 +30,8 @@ __global__ void __launch_bounds__(256)
 causal_conv_rows_kernel(const float* x, int x_stride, const float* __restrict__ w, int taps, int channels,
                         const int* __restrict__ req_of_tok, const int* __restrict__ cu_q,
                         const int* __restrict__ slots, const float* state, size_t state_stride,
-                        size_t state_offset, int add_input, int silu, TO* __restrict__ out, int out_stride) {
+                        size_t state_offset, int add_input, int silu, int renew, TO* __restrict__ out,
+                        int out_stride) {
     const int t = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= channels) return;
@@ -49,6 +51,11 @@ causal_conv_rows_kernel(const float* x, int x_stride, const float* __restrict__ 
             acc = fmaf(w[(size_t)c * taps + j], v, acc);
         }
         y += acc;
+        if (renew && taps > 1) {                           // one token a request: nobody else reads these rows
+            float* rows = const_cast<float*>(kept);
+            for (int j = 0; j + 2 < taps; ++j) rows[(size_t)j * channels + c] = rows[(size_t)(j + 1) * channels + c];
+            rows[(size_t)(taps - 2) * channels + c] = cur;
+        }
     }
     if (silu) y = y / (1.0f + expf(-y));
     out[(size_t)t * out_stride + c] = from_f32<TO>(y);
@@ -73,20 +80,34 @@ conv_tail_store_kernel(const float* x, int x_stride, int taps, int channels, con
     for (int j = 0; j < keep; ++j) kept[(size_t)j * channels + c] = rows[j];
 }
 
-// one block per row; a warp takes the groups in turn
+// `wpg` warps share a group (each a strided share of its elements; their sums of squares meet in
+// shared memory in a fixed order); the block's warps take the groups `blockDim / 32 / wpg` at a time.
 template <typename TO, bool ADD>
 __global__ void __launch_bounds__(256)
 group_norm_rows_kernel(const float* x, const float* __restrict__ w, const int* __restrict__ rows, int groups,
-                       int n, float eps, TO* __restrict__ out, float* residual, int res_stride) {
+                       int n, float eps, TO* __restrict__ out, float* residual, int res_stride, int wpg) {
+    __shared__ float part[8];
     const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * n;
-    const int per = n / groups;
-    for (int g = warp; g < groups; g += nw) {
+    const int per = n / groups, at_once = nw / wpg, sub = warp % wpg;
+    for (int g0 = 0; g0 < groups; g0 += at_once) {
+        const int g = g0 + warp / wpg;
+        const bool live = g < groups;
         const float* xg = xr + (size_t)g * per;
         float ss = 0.0f;
-        for (int e = lane; e < per; e += 32) ss = fmaf(xg[e], xg[e], ss);
-        const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)per + eps);
-        for (int e = lane; e < per; e += 32) {
+        if (live)
+            for (int e = sub * 32 + lane; e < per; e += wpg * 32) ss = fmaf(xg[e], xg[e], ss);
+        ss = warp_sum(ss);
+        if (wpg > 1) {
+            if (lane == 0) part[warp] = ss;
+            __syncthreads();
+            ss = 0.0f;
+            for (int i = 0; i < wpg; ++i) ss += part[(warp / wpg) * wpg + i];
+            __syncthreads();                              // before the next groups' sums land
+        }
+        if (!live) continue;
+        const float inv = 1.0f / sqrtf(ss / (float)per + eps);
+        for (int e = sub * 32 + lane; e < per; e += wpg * 32) {
             const float y = xg[e] * inv * w[g * per + e];
             if constexpr (ADD) residual[(size_t)r * res_stride + g * per + e] += y;
             else out[(size_t)r * n + g * per + e] = from_f32<TO>(y);
@@ -136,7 +157,7 @@ glu_rows_kernel(const float* gu, int inter, size_t total, int interleaved, int k
 extern "C" int ti_causal_conv_rows(const float* x, int x_stride, const float* w, int taps, int channels, int rows,
                                    const int* req_of_tok, const int* cu_q, const int* slots, const float* state,
                                    long long state_stride, long long state_offset, int add_input, int silu,
-                                   void* out, int out_dtype, int out_stride, void* stream) {
+                                   int renew, void* out, int out_dtype, int out_stride, void* stream) {
     if (rows == 0 || channels == 0) return 0;
     TI_REQUIRE(taps >= 0 && taps <= MAX_TAPS, "causal_conv_rows: %d taps (at most %d)", taps, MAX_TAPS);
     TI_REQUIRE(taps <= 1 || state != nullptr, "causal_conv_rows: a convolution over time needs the state");
@@ -145,11 +166,11 @@ extern "C" int ti_causal_conv_rows(const float* x, int x_stride, const float* w,
     if (out_dtype == TI_BF16)
         causal_conv_rows_kernel<bf16><<<grid, 256, 0, s>>>(x, x_stride, w, taps, channels, req_of_tok, cu_q, slots, state,
                                                            (size_t)state_stride, (size_t)state_offset, add_input, silu,
-                                                           (bf16*)out, out_stride);
+                                                           renew, (bf16*)out, out_stride);
     else if (out_dtype == TI_F32)
         causal_conv_rows_kernel<float><<<grid, 256, 0, s>>>(x, x_stride, w, taps, channels, req_of_tok, cu_q, slots, state,
                                                             (size_t)state_stride, (size_t)state_offset, add_input, silu,
-                                                            (float*)out, out_stride);
+                                                            renew, (float*)out, out_stride);
     else return ti_fail("causal_conv_rows: output dtype code %d", out_dtype);
     return ti_check_launch("causal_conv_rows");
 }
@@ -170,15 +191,16 @@ extern "C" int ti_group_norm_rows(const float* x, const float* w, const int* row
     if (num_rows == 0) return 0;
     TI_REQUIRE(groups >= 1 && n % groups == 0, "group_norm_rows: %d elements do not fall into %d equal groups", n, groups);
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = groups >= 8 ? 256 : groups * 32;
+    const int wpg = groups >= 8 ? 1 : 8 / groups;         // warps a group: 8, 4, 2, 2, 1, 1, 1, 1 for 1 to 8 groups
+    const int threads = (groups >= 8 ? 8 : groups) * wpg * 32;
     if (residual != nullptr) {
         TI_REQUIRE(rows == nullptr, "group_norm_rows: rows are not gathered when adding to a residual");
         group_norm_rows_kernel<float, true><<<num_rows, threads, 0, s>>>(x, w, rows, groups, n, eps, nullptr, residual,
-                                                                        res_stride);
+                                                                        res_stride, wpg);
     } else if (out_dtype == TI_BF16) {
-        group_norm_rows_kernel<bf16, false><<<num_rows, threads, 0, s>>>(x, w, rows, groups, n, eps, (bf16*)out, nullptr, 0);
+        group_norm_rows_kernel<bf16, false><<<num_rows, threads, 0, s>>>(x, w, rows, groups, n, eps, (bf16*)out, nullptr, 0, wpg);
     } else if (out_dtype == TI_F32) {
-        group_norm_rows_kernel<float, false><<<num_rows, threads, 0, s>>>(x, w, rows, groups, n, eps, (float*)out, nullptr, 0);
+        group_norm_rows_kernel<float, false><<<num_rows, threads, 0, s>>>(x, w, rows, groups, n, eps, (float*)out, nullptr, 0, wpg);
     } else {
         return ti_fail("group_norm_rows: output dtype code %d", out_dtype);
     }

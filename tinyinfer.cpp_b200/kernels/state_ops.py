@@ -48,8 +48,8 @@ class StateOps:
         if self._state_lib is None:
             b = load_library("state")
             b.ti_last_error.restype = ctypes.c_char_p
-            b.ti_causal_conv_rows.argtypes = [_vp, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _vp, _i,
-                                              _i, _vp]
+            b.ti_causal_conv_rows.argtypes = [_vp, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _vp,
+                                              _i, _i, _vp]
             b.ti_conv_tail_store.argtypes = [_vp, _i, _i, _i, _vp, _vp, _i, _vp, _ll, _ll, _vp]
             b.ti_group_norm_rows.argtypes = [_vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _vp, _i, _vp]
             b.ti_depth_mix.argtypes = [_vp, _vp, _ll, _i, _vp, _vp]
@@ -71,11 +71,13 @@ class StateOps:
             raise KernelError(msg)
 
     # ---- short convolutions over time ----------------------------------------------------------
-    def causal_conv(self, x, w, step, state, state_offset, out, add_input=False, silu=False):
+    def causal_conv(self, x, w, step, state, state_offset, out, add_input=False, silu=False, renew=False):
         """``out[t, c] = [x[t, c] +] sum_j w[c, j] x[t - taps + 1 + j, c]``, then silu if asked, over
         float32 rows ``x`` (a column slice is fine).  Rows before a request's portion come from
         ``state`` (a ``StateView``: per slot ``[taps - 1, channels]`` floats from ``state_offset``
-        on, the newest row last).  ``w`` None: the rows are converted (and nothing else)."""
+        on, the newest row last).  ``w`` None: the rows are converted (and nothing else).
+        ``renew``: the kept rows become the requests' last inputs after this step, in the same
+        launch where every request brings one token, else by ``conv_tail_store`` behind it."""
         t, c = x.shape
         taps = 0 if w is None else w.shape[1]
         self._want(x.dtype == torch.float32 and x.stride(1) == 1 and out.stride(1) == 1
@@ -86,11 +88,15 @@ class StateOps:
         self._want(taps <= 1 or (st is not None and st.dtype == torch.float32
                                  and st[0].numel() >= state_offset + (taps - 1) * c),
                    "causal_conv: the state must hold taps - 1 float32 rows")
+        renew = bool(renew) and taps > 1 and state.writes
+        in_place = renew and step.max_q_len == 1 and step.num_requests == t
         self._st(self.state_lib.ti_causal_conv_rows(
             x.data_ptr(), x.stride(0), _ptr(w), taps, c, t, step.req_of_tok.data_ptr(), step.cu_q.data_ptr(),
             _ptr(state.slots) if state is not None else None, _ptr(st), st.stride(0) if st is not None else 0,
-            int(state_offset), int(bool(add_input)), int(bool(silu)), out.data_ptr(), _CODE[out.dtype],
+            int(state_offset), int(bool(add_input)), int(bool(silu)), int(in_place), out.data_ptr(), _CODE[out.dtype],
             out.stride(0), self._stream()))
+        if renew and not in_place:
+            self.conv_tail_store(x, taps, step, state, state_offset)
 
     def conv_tail_store(self, x, taps, step, state, state_offset):
         """The state's ``taps - 1`` kept rows of every request become its last inputs after this

@@ -114,9 +114,7 @@ class OutputNormBlock(Part):
                 ops.depth_mix(x, hist, 0)                      # X_0: what enters the first layer
         h = torch.empty((t, self.hidden_size), dtype=step.act_dtype, device=dev)
         kept = cache["conv"] if self.conv_taps > 1 else None
-        ops.causal_conv(x, self.conv_w, step, kept, 0, h, add_input=True)
-        if kept is not None:
-            ops.conv_tail_store(x, self.conv_taps, step, kept, 0)  # before x moves on
+        ops.causal_conv(x, self.conv_w, step, kept, 0, h, add_input=True, renew=True)     # kept rows renewed before x moves on
         y = torch.zeros((t, self.hidden_size), dtype=torch.float32, device=dev)
         self.mixer.forward(ops, h, y, step, cache.child("mixer"))
         self.mixer_norm.add_to(ops, y, x)

@@ -93,8 +93,7 @@ class GatedDeltaMixer(Part):
         proj = torch.empty((t, self.w_in.shape[0]), dtype=torch.float32, device=dev)
         ops.linear(h, self.w_in, proj)
         qkv = torch.empty((t, c), dtype=torch.float32, device=dev)
-        ops.causal_conv(proj[:, :c], self.conv_w, step, cache, self.state_floats, qkv, silu=True)
-        ops.conv_tail_store(proj[:, :c], self.conv_taps, step, cache, self.state_floats)
+        ops.causal_conv(proj[:, :c], self.conv_w, step, cache, self.state_floats, qkv, silu=True, renew=True)
         out = torch.empty((t, nv), dtype=h.dtype, device=dev)
         ops.matrix_state("delta", qkv[:, :nk], qkv[:, nk:2 * nk], qkv[:, 2 * nk:], proj[:, c + nv:c + nv + nh],
                          proj[:, c + nv + nh:c + nv + 2 * nh], self.a_log, self.dt_bias, step, cache, out,
