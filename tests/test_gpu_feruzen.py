@@ -190,7 +190,8 @@ def _ffn_part(ops, mlp, width, w):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("sizes", [(1, 48, 40, 1.5), (9, 36, 8, 0.25), (70, 128, 192, 2.0), (300, 64, 96, 7.0), (3, 40, 24, 1.0)])
+@pytest.mark.parametrize("sizes", [(1, 48, 40, 1.5), (9, 36, 8, 0.25), (70, 128, 192, 2.0), (300, 64, 96, 7.0), (3, 40, 24, 1.0),
+                                   (5, 64, 96, 1.5), (40, 128, 64, 0.5)])
 def test_clamped_feed_forward(ops, sizes, dtype):
     """Inputs large enough that the gate reaches its upper clamp (and stays free below) and the other
     branch both of its clamps."""

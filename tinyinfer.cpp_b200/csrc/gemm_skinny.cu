@@ -13,6 +13,7 @@
 // Epilogues: store, accumulate into C (the residual stream), or SwiGLU: W holds, in every strip,
 // 8 gate rows followed by their 8 up rows, and out[m, j] = silu(gate_j) * up_j in bfloat16.
 #include "common.cuh"
+#include "glu.cuh"
 
 namespace {
 
@@ -156,9 +157,10 @@ gemm_skinny_kernel(const bf16* a, const bf16* __restrict__ w, float* __restrict_
                     gate += part[wp][i][tok];
                     up += part[wp][(i + 8) % ROWS][tok];
                 }
-                if (n0 + i + 8 < n)
-                    out_act[(size_t)tok * ld_act + col] =
-                        __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+                // act_q (the clamped gate's factor inside the sigmoid) other than 0: that activation, with the limit act_p
+                const float y = act_q != 0.0f ? glu_activation(GLU_CLAMPED, gate, up, act_p, act_q)
+                                              : gate / (1.0f + expf(-gate)) * up;
+                if (n0 + i + 8 < n) out_act[(size_t)tok * ld_act + col] = __float2bfloat16_rn(y);
             }
         }
     } else {
@@ -229,6 +231,17 @@ extern "C" int ti_gemm_skinny(const void* a, const void* w, float* c, void* out_
                               int k, int lda, int ldw, int ldc, int ld_act, int mode, void* stream) {
     TI_REQUIRE(mode >= MODE_STORE && mode <= MODE_SWIGLU, "gemm_skinny: mode %d", mode);
     return skinny(a, w, c, out_act, m, n, k, lda, ldw, ldc, ld_act, mode, 0.0f, 0.0f, stream);
+}
+
+// out_act[m, n/2] (bfloat16) = act(gate, up) over strips of 8 gate and 8 up rows of w, with the gated activation
+// `glu_kind` of glu.cuh in the epilogue.
+extern "C" int ti_gemm_skinny_glu(const void* a, const void* w, void* out_act, int m, int n, int k, int lda, int ldw,
+                                  int ld_act, int glu_kind, float glu_limit, float glu_alpha, void* stream) {
+    TI_REQUIRE(glu_kind == GLU_SILU || (glu_kind == GLU_CLAMPED && glu_alpha != 0.0f),
+               "gemm_skinny_glu: activation %d (the clamped gate needs its factor)", glu_kind);
+    const bool clamped = glu_kind == GLU_CLAMPED;
+    return skinny(a, w, nullptr, out_act, m, n, k, lda, ldw, 0, ld_act, MODE_SWIGLU, clamped ? glu_limit : 0.0f,
+                  clamped ? glu_alpha : 0.0f, stream);
 }
 
 // out_act[m, n] (bfloat16) = xielu(a w^T): act_p z^2 + z/2 for z > 0, act_q (exp(z) - 1 - z) + z/2 otherwise

@@ -252,6 +252,7 @@ class CudaOps(MixerOps, StateOps):
                                                   _vp, _vp]
             b.ti_gemm_tcgen05_grouped_glu.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _f, _f,
                                                       _vp, _vp]
+            b.ti_gemm_skinny_glu.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]
             b.ti_gemm_tcgen05_glu.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _vp]
             b.ti_gemm_tcgen05_2sm.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]
             qkv_args = [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i,
@@ -571,7 +572,14 @@ class CudaOps(MixerOps, StateOps):
         inter = w_down.shape[1]
         interleaved = bool(getattr(w_gate_up, "_ti_interleaved", False))
         y = torch.empty((m, inter), dtype=h.dtype, device=h.device)
-        if (interleaved and m > 64 and h.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16
+        if (interleaved and h.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and float(alpha) != 0.0
+                and h.data_ptr() % 16 == 0
+                and self.bf16.ti_gemm_skinny_supported(m, 2 * inter, k, h.stride(0), w_gate_up.stride(0))):
+            # few rows: the activation in the epilogue of the product that streams the weights once
+            self._ok(self.bf16.ti_gemm_skinny_glu(
+                h.data_ptr(), w_gate_up.data_ptr(), y.data_ptr(), m, 2 * inter, k, h.stride(0), w_gate_up.stride(0),
+                y.stride(0), GLU_KINDS[kind], float(limit), float(alpha), self._stream()), self.bf16)
+        elif (interleaved and m > 64 and h.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16
                 and inter % 8 == 0 and h.data_ptr() % 16 == 0 and self.bf16.ti_gemm_tcgen05_supported(
                     m, 2 * inter, k, h.stride(0), w_gate_up.stride(0), 0, 2)):
             # many rows: the activation in the epilogue of the tcgen05 product
