@@ -12,7 +12,9 @@ A plan is plain data:
                       under which their tensors are stored.
 * ``ScheduleEntry`` : one execution of a layer.  The schedule is a list; it may
                       name a layer twice, and an entry may read the cache slot
-                      that another entry writes.
+                      that another entry writes.  An entry may first run the
+                      plan's junction (a part that renews the residual stream
+                      from itself and the embedding output).
 """
 from __future__ import annotations
 
@@ -46,6 +48,8 @@ class LayerPlan:
     mixer_norm: PartSpec
     ffn_norm: Optional[PartSpec]         # None: the block has one norm (both sublayers read it)
     names: Mapping[str, str]
+    mixer_post_norm: Optional[PartSpec] = None   # blocks that also norm a sublayer's output (``sandwich``)
+    ffn_post_norm: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
@@ -53,11 +57,14 @@ class ScheduleEntry:
     """Run layer ``layer`` using cache slot ``cache_slot``.
 
     ``writes_cache`` is False for an entry that only reads what an earlier
-    entry of the same step wrote into that slot.
+    entry of the same step wrote into that slot.  ``enter`` (a number) runs the
+    plan's junction with that number on the residual stream right before the layer:
+    the first layer of a pass over a run of layers that is walked several times.
     """
     layer: int
     cache_slot: int
     writes_cache: bool = True
+    enter: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -72,9 +79,12 @@ class ModelPlan:
     final_norm: PartSpec
     head: PartSpec
     names: Mapping[str, str]
+    junction: Optional[PartSpec] = None      # what schedule entries with ``enter`` run; tensors under names["junction"]
 
     def __post_init__(self) -> None:
         n = len(self.layers)
+        if self.junction is None and any(e.enter is not None for e in self.schedule):
+            raise ValueError("a schedule entry enters a pass, but the plan has no junction")
         writers: dict[int, int] = {}
         for pos, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < n:

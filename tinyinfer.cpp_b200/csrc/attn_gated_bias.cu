@@ -2,7 +2,8 @@
 // tokens, value heads of their own size and an output gate, on the CUDA cores.
 //
 //  * embed_sinusoid: x[t] = table[token[t]] * scale + s(pos[t]), where s(p)[2i] = sin(p f_i),
-//    s(p)[2i + 1] = cos(p f_i) and f_i comes from the caller (float32).
+//    s(p)[2i + 1] = cos(p f_i) and f_i comes from the caller (float32); without frequencies the scaled
+//    row alone.
 //  * qkv_bias_norm_store: adds the projection's bias, brings every query and key head to unit
 //    root mean square (times a weight, if one is given), writes keys and values once per kv head
 //    into the token's page and the queries for the attention kernel.
@@ -31,8 +32,11 @@ embed_sinusoid_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
     const TW* row = table + (size_t)ids[t] * width;
     const float pos = (float)positions[t];
     for (int d = threadIdx.x; d < width; d += blockDim.x) {
-        const float angle = pos * freq[d >> 1];
-        const float wave = (d & 1) ? cosf(angle) : sinf(angle);
+        float wave = 0.0f;                      // no frequencies: the scaled row alone
+        if (freq != nullptr) {
+            const float angle = pos * freq[d >> 1];
+            wave = (d & 1) ? cosf(angle) : sinf(angle);
+        }
         out[(size_t)t * width + d] = to_f32(row[d]) * scale + wave;
     }
 }

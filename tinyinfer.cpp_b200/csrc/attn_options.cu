@@ -9,6 +9,11 @@
 //    rotated) | latent of `rank` | one rotated key part of dr]: the latent is normed (RMS, a weight
 //    per element) and stored with the turned key part as ONE row of the token's page; the plain
 //    query parts and the turned query parts go out separately.
+//  * qkv_turn_store: the same columns without any norm: the first `rot` elements of every query and key
+//    head are turned by the token's position (pairs of neighbours, or element i with i + rot/2), the
+//    first `v_rot` elements of every value head by frequencies of their own, keys and values go into
+//    the token's page and the queries out.  turn_rows turns the heads of finished rows by plus or minus
+//    their position (the way back for outputs over turned values) and multiplies by sigmoid(gate).
 //  * head_project: out[t, h, :] = in[t, h, :] W[h] with a matrix [n_in, n_out] per head.
 //  * attention_options: one block per (token, query head).  Token i sees key j <= i when j is not
 //    behind the window (i - j < window) and not in an earlier chunk (j >= floor(i / chunk) *
@@ -35,6 +40,81 @@ __device__ __forceinline__ float turned(const float* x, int j, float pos, const 
     sincosf(pos * inv_freq[j >> 1], &s, &c);
     const float a = x[j] * unit, b = x[j ^ 1] * unit;
     return (j & 1) ? a * c + b * s : a * c - b * s;
+}
+
+// element j of a head x whose first `rot` elements are turned by `pos`: neighbours (2i, 2i + 1) form pair
+// i, or, `halves`, elements (i, i + rot/2); both the sine and the cosine are multiplied by `mag`
+__device__ __forceinline__ float turned_at(const float* x, int j, int rot, int halves, float pos,
+                                           const float* __restrict__ inv_freq, float mag) {
+    if (j >= rot) return x[j];
+    const int half = rot >> 1;
+    const int pair = halves ? (j < half ? j : j - half) : (j >> 1);
+    const bool second = halves ? j >= half : (j & 1);
+    const int other = halves ? (second ? j - half : j + half) : (j ^ 1);
+    float s, c;
+    sincosf(pos * inv_freq[pair], &s, &c);
+    s *= mag;
+    c *= mag;
+    return second ? x[j] * c + x[other] * s : x[j] * c - x[other] * s;
+}
+
+template <typename TQ, typename TC>
+__global__ void __launch_bounds__(256)
+qkv_turn_store_kernel(const float* proj, int stride, const float* __restrict__ inv_freq, int rot, int halves, float mag,
+                      const float* __restrict__ v_inv_freq, int v_rot, int v_halves,
+                      const int* __restrict__ positions, const int* __restrict__ req_of_tok,
+                      const int* __restrict__ block_table, int bt_stride, TC* __restrict__ pages, int num_pages,
+                      int page_size, int write_kv, int num_heads, int num_kv_heads, int dk, int dv,
+                      TQ* __restrict__ q_out, int* __restrict__ status) {
+    const int t = blockIdx.x;
+    const int nq = num_heads * dk, nk = num_kv_heads * dk, nv = num_kv_heads * dv;
+    const float* row = proj + (size_t)t * stride;
+    const int pos_i = positions[t];
+    const float pos = (float)pos_i;
+    for (int e = threadIdx.x; e < nq; e += blockDim.x) {
+        const int j = e % dk;
+        q_out[(size_t)t * nq + e] = from_f32<TQ>(turned_at(row + (e - j), j, rot, halves, pos, inv_freq, mag));
+    }
+    if (!write_kv) return;
+    const int page = block_table[(size_t)req_of_tok[t] * bt_stride + pos_i / page_size];
+    if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0) atomicCAS(status, 0, TI_ERR_BAD_PAGE);
+        return;
+    }
+    const int slot = pos_i % page_size;
+    TC* base = pages + (size_t)page * num_kv_heads * page_size * (dk + dv);
+    const float* krow = row + nq;
+    for (int e = threadIdx.x; e < nk; e += blockDim.x) {
+        const int j = e % dk, g = e / dk;
+        base[((size_t)g * page_size + slot) * dk + j] =
+            from_f32<TC>(turned_at(krow + (e - j), j, rot, halves, pos, inv_freq, mag));
+    }
+    TC* vbase = base + (size_t)num_kv_heads * page_size * dk;
+    const float* vrow = krow + nk;
+    for (int e = threadIdx.x; e < nv; e += blockDim.x) {
+        const int j = e % dv, g = e / dv;
+        vbase[((size_t)g * page_size + slot) * dv + j] =
+            from_f32<TC>(turned_at(vrow + (e - j), j, v_rot, v_halves, pos, v_inv_freq, 1.0f));
+    }
+}
+
+// x[t, h, :] turned by sign * position over its first `rot` elements, then times sigmoid(gate[t, h * n + j])
+template <typename T>
+__global__ void __launch_bounds__(256)
+turn_rows_kernel(const T* x, const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot,
+                 int halves, float sign, const float* gate, int gate_stride, int num_heads, int n, T* out) {
+    extern __shared__ float head_rows[];               // the token's heads in float32
+    const int t = blockIdx.x, width = num_heads * n;
+    const T* src = x + (size_t)t * width;
+    for (int e = threadIdx.x; e < width; e += blockDim.x) head_rows[e] = to_f32(src[e]);
+    __syncthreads();
+    const float pos = sign * (float)positions[t];
+    for (int e = threadIdx.x; e < width; e += blockDim.x) {
+        const int j = e % n;
+        float y = turned_at(head_rows + (e - j), j, rot, halves, pos, inv_freq, 1.0f);
+        if (gate) y *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + e]));
+        out[(size_t)t * width + e] = from_f32<T>(y);
+    }
 }
 
 template <typename TQ, typename TC>
@@ -110,22 +190,23 @@ qk_rownorm_rope_store_kernel(const float* proj, int stride, const float* __restr
 
 template <typename TQ, typename TC>
 __global__ void __launch_bounds__(256)
-latent_prepare_kernel(const float* proj, int stride, const float* __restrict__ latent_weight, float eps,
-                      const float* __restrict__ inv_freq, const int* __restrict__ positions,
+latent_prepare_kernel(const float* qproj, int q_stride, const float* proj, int stride,
+                      const float* __restrict__ latent_weight, float eps,
+                      const float* __restrict__ inv_freq, float mag, const int* __restrict__ positions,
                       const int* __restrict__ req_of_tok, const int* __restrict__ block_table, int bt_stride,
                       TC* __restrict__ pages, int num_pages, int page_size, int num_heads, int dk, int dr,
                       int rank, TQ* __restrict__ q_plain, TQ* __restrict__ q_full, int* __restrict__ status) {
     __shared__ float scratch[32];
     const int t = blockIdx.x;
     const int qh = dk + dr, nq = num_heads * qh, row_len = rank + dr;
-    const float* row = proj + (size_t)t * stride;
+    const float* row = qproj + (size_t)t * q_stride;
     const int pos_i = positions[t];
     const float pos = (float)pos_i;
     for (int e = threadIdx.x; e < nq; e += blockDim.x) {
         const int j = e % qh, h = e / qh;
         if (j < dk) q_plain[((size_t)t * num_heads + h) * dk + j] = from_f32<TQ>(row[e]);
         else q_full[((size_t)t * num_heads + h) * row_len + rank + (j - dk)] =
-                 from_f32<TQ>(turned(row + h * qh + dk, j - dk, pos, inv_freq, 1.0f));
+                 from_f32<TQ>(mag * turned(row + h * qh + dk, j - dk, pos, inv_freq, 1.0f));
     }
     const int page = block_table[(size_t)req_of_tok[t] * bt_stride + pos_i / page_size];
     if (page < 0 || page >= num_pages) {
@@ -133,14 +214,14 @@ latent_prepare_kernel(const float* proj, int stride, const float* __restrict__ l
         return;
     }
     TC* dst = pages + ((size_t)page * page_size + pos_i % page_size) * row_len;
-    const float* lat = row + nq;
+    const float* lat = proj + (size_t)t * stride;
     float ss = 0.0f;
     for (int e = threadIdx.x; e < rank; e += blockDim.x) ss = fmaf(lat[e], lat[e], ss);
     const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)rank + eps);
     for (int e = threadIdx.x; e < rank; e += blockDim.x)
         dst[e] = from_f32<TC>(lat[e] * inv * (latent_weight ? latent_weight[e] : 1.0f));
     for (int e = threadIdx.x; e < dr; e += blockDim.x)
-        dst[rank + e] = from_f32<TC>(turned(lat + rank, e, pos, inv_freq, 1.0f));
+        dst[rank + e] = from_f32<TC>(mag * turned(lat + rank, e, pos, inv_freq, 1.0f));
 }
 
 // out[t, h, n] = sum_k in[t, h, k] * w[h, k, n]; a block has 16 tokens of one head and 128 columns.
@@ -474,8 +555,10 @@ extern "C" int ti_qk_rownorm_rope_store(const float* proj, int stride, const flo
     return ti_check_launch("qk_rownorm_rope_store");
 }
 
-extern "C" int ti_latent_prepare(const float* proj, int stride, const float* latent_weight, float eps,
-                                 const float* inv_freq, const int* positions, const int* req_of_tok,
+// `qproj` holds a token's query heads of (dk plain | dr rotated), `proj` its latent of `rank` and the key part of dr
+extern "C" int ti_latent_prepare(const float* qproj, int q_stride, const float* proj, int stride,
+                                 const float* latent_weight, float eps,
+                                 const float* inv_freq, float mag, const int* positions, const int* req_of_tok,
                                  const int* block_table, int bt_stride, void* pages, int cache_dtype,
                                  int num_pages, int page_size, int num_tokens, int num_heads, int dk, int dr,
                                  int rank, void* q_plain, void* q_full, int q_dtype, int* status,
@@ -486,11 +569,54 @@ extern "C" int ti_latent_prepare(const float* proj, int stride, const float* lat
     cudaStream_t s = (cudaStream_t)stream;
 #define CALL(TQ, TC)                                                                              \
     latent_prepare_kernel<TQ, TC><<<num_tokens, 256, 0, s>>>(                                      \
-        proj, stride, latent_weight, eps, inv_freq, positions, req_of_tok, block_table, bt_stride,  \
+        qproj, q_stride, proj, stride, latent_weight, eps, inv_freq, mag, positions, req_of_tok, block_table, bt_stride,  \
         (TC*)pages, num_pages, page_size, num_heads, dk, dr, rank, (TQ*)q_plain, (TQ*)q_full, status)
     TI_DISPATCH_QC(q_dtype, cache_dtype, CALL)
 #undef CALL
     return ti_check_launch("latent_prepare");
+}
+
+extern "C" int ti_qkv_turn_store(const float* proj, int stride, const float* inv_freq, int rot, int halves, float mag,
+                                 const float* v_inv_freq, int v_rot, int v_halves, const int* positions,
+                                 const int* req_of_tok, const int* block_table, int bt_stride, void* pages,
+                                 int cache_dtype, int num_pages, int page_size, int write_kv, int num_tokens,
+                                 int num_heads, int num_kv_heads, int dk, int dv, void* q_out, int q_dtype,
+                                 int* status, void* stream) {
+    if (num_tokens == 0) return 0;
+    TI_REQUIRE(rot >= 0 && rot <= dk && rot % 2 == 0, "qkv_turn_store: rotated width %d must be even and at most "
+               "the head size %d", rot, dk);
+    TI_REQUIRE(v_rot >= 0 && v_rot <= dv && v_rot % 2 == 0, "qkv_turn_store: rotated width %d of the values must be "
+               "even and at most their head size %d", v_rot, dv);
+    TI_REQUIRE((rot == 0 || inv_freq != nullptr) && (v_rot == 0 || v_inv_freq != nullptr),
+               "qkv_turn_store: a rotation needs its frequencies");
+    cudaStream_t s = (cudaStream_t)stream;
+#define CALL(TQ, TC)                                                                              \
+    qkv_turn_store_kernel<TQ, TC><<<num_tokens, 256, 0, s>>>(                                      \
+        proj, stride, inv_freq, rot, halves, mag, v_inv_freq, v_rot, v_halves, positions, req_of_tok, \
+        block_table, bt_stride, (TC*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads, dk, dv, \
+        (TQ*)q_out, status)
+    TI_DISPATCH_QC(q_dtype, cache_dtype, CALL)
+#undef CALL
+    return ti_check_launch("qkv_turn_store");
+}
+
+extern "C" int ti_turn_rows(const void* x, int dtype, const int* positions, const float* inv_freq, int rot, int halves,
+                            float sign, const float* gate, int gate_stride, int num_tokens, int num_heads, int n,
+                            void* out, void* stream) {
+    if (num_tokens == 0 || num_heads == 0) return 0;
+    TI_REQUIRE(rot >= 0 && rot <= n && rot % 2 == 0, "turn_rows: rotated width %d must be even and at most %d", rot, n);
+    TI_REQUIRE(rot == 0 || inv_freq != nullptr, "turn_rows: a rotation needs its frequencies");
+    const size_t smem = (size_t)num_heads * n * sizeof(float);
+    TI_REQUIRE(smem <= 48 * 1024, "turn_rows: rows of %d elements are more than the kernel stages", num_heads * n);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == TI_BF16)
+        turn_rows_kernel<bf16><<<num_tokens, 256, smem, s>>>((const bf16*)x, positions, inv_freq, rot, halves, sign, gate,
+                                                            gate_stride, num_heads, n, (bf16*)out);
+    else if (dtype == TI_F32)
+        turn_rows_kernel<float><<<num_tokens, 256, smem, s>>>((const float*)x, positions, inv_freq, rot, halves, sign,
+                                                             gate, gate_stride, num_heads, n, (float*)out);
+    else return ti_fail("turn_rows: dtype code %d", dtype);
+    return ti_check_launch("turn_rows");
 }
 
 extern "C" int ti_head_project(const void* in, int in_dtype, int in_stride_t, int in_stride_h, const void* w,

@@ -248,13 +248,22 @@ moe_grouped_kernel(const bf16* a, int lda, const int* __restrict__ sorted_slot,
     }
 }
 
+// A slot whose index is not below `experts` names an identity expert: its row is the token's input times
+// the slot's weight (`ids` null: there are none).
 __global__ void moe_combine_kernel(const float* __restrict__ rows, int top, int width, int num_tokens,
-                                   float* __restrict__ residual, int res_stride) {
+                                   float* __restrict__ residual, int res_stride, const int* __restrict__ ids,
+                                   int experts, const float* __restrict__ id_weights, const bf16* __restrict__ h,
+                                   int h_stride) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)num_tokens * width) return;
     const int t = (int)(i / width), c = (int)(i % width);
     float total = 0.0f;
-    for (int s = 0; s < top; ++s) total += rows[((size_t)t * top + s) * width + c];
+    for (int s = 0; s < top; ++s) {
+        if (ids != nullptr && ids[t * top + s] >= experts)
+            total = fmaf(id_weights[t * top + s], __bfloat162float(h[(size_t)t * h_stride + c]), total);
+        else
+            total += rows[((size_t)t * top + s) * width + c];
+    }
     residual[(size_t)t * res_stride + c] += total;
 }
 
@@ -329,13 +338,21 @@ __global__ void moe_gather_scaled_kernel(const bf16* __restrict__ h, int h_strid
 
 __global__ void moe_combine_rows_kernel(const float* __restrict__ rows, const int* __restrict__ pos_of_pair, int top,
                                         int width, int num_tokens, float* __restrict__ residual, int res_stride,
-                                        const float* __restrict__ weights) {
+                                        const float* __restrict__ weights, const int* __restrict__ ids, int experts,
+                                        const float* __restrict__ id_weights, const bf16* __restrict__ h, int h_stride) {
     const int quads = width >> 2;                      // width is a multiple of 8 on this path
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)num_tokens * quads) return;
     const int t = (int)(i / quads), c = (int)(i % quads) * 4;
     float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     for (int s = 0; s < top; ++s) {
+        if (ids != nullptr && ids[t * top + s] >= experts) {      // an identity expert: the input times the weight
+            const float w = id_weights[t * top + s];
+            const bf16* x = h + (size_t)t * h_stride + c;
+            total.x = fmaf(w, __bfloat162float(x[0]), total.x); total.y = fmaf(w, __bfloat162float(x[1]), total.y);
+            total.z = fmaf(w, __bfloat162float(x[2]), total.z); total.w = fmaf(w, __bfloat162float(x[3]), total.w);
+            continue;
+        }
         const float4 v = *reinterpret_cast<const float4*>(rows + (size_t)pos_of_pair[t * top + s] * width + c);
         const float w = weights != nullptr ? weights[t * top + s] : 1.0f;            // a pair's weight on its expert's output
         total.x = fmaf(w, v.x, total.x); total.y = fmaf(w, v.y, total.y);
@@ -367,12 +384,14 @@ extern "C" int ti_moe_gather_scaled(const void* h, int h_stride, const int* row_
 }
 
 extern "C" int ti_moe_combine_rows(const float* rows, const int* pos_of_pair, int top, int width, int num_tokens,
-                                   float* residual, int res_stride, const float* weights, void* stream) {
+                                   float* residual, int res_stride, const float* weights, const int* ids, int experts,
+                                   const float* id_weights, const void* h, int h_stride, void* stream) {
     TI_REQUIRE(width % 4 == 0 && ((uintptr_t)rows) % 16 == 0, "moe_combine_rows: rows of four-float groups, 16-byte aligned");
     const size_t total = (size_t)num_tokens * (width / 4);
     if (total == 0) return 0;
     moe_combine_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        rows, pos_of_pair, top, width, num_tokens, residual, res_stride, weights);
+        rows, pos_of_pair, top, width, num_tokens, residual, res_stride, weights, ids, experts, id_weights,
+        (const bf16*)h, h_stride);
     return ti_check_launch("moe_combine_rows");
 }
 
@@ -386,7 +405,7 @@ extern "C" int ti_moe_grouped(const void* h, int h_stride, const void* w_gate_up
                               const void* w_down, const int* ids, const float* weights, int num_tokens,
                               int top, int experts, int width, int ff, int* sorted_slot, int* tiles,
                               int* meta, void* y_sorted, float* out_rows, float* residual,
-                              int res_stride, int act, float act_limit, float act_alpha, void* stream) {
+                              int res_stride, int act, float act_limit, float act_alpha, int identity, void* stream) {
     if (num_tokens == 0) return 0;
     TI_REQUIRE(ti_moe_grouped_supported(width, ff, experts),
                "moe_grouped: width %d and expert size %d must be multiples of 32", width, ff);
@@ -413,7 +432,9 @@ extern "C" int ti_moe_grouped(const void* h, int h_stride, const void* w_gate_up
         (const bf16*)y_sorted, ff, sorted_slot, tiles, meta, top, (const bf16*)w_down, 0, width, ff,
         nullptr, nullptr, out_rows, 0, 0.0f, 0.0f);
     const size_t total = (size_t)num_tokens * width;
+    // `identity`: slots may name identity experts (an index not below `experts`)
     moe_combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(out_rows, top, width, num_tokens,
-                                                                       residual, res_stride);
+                                                                       residual, res_stride, identity ? ids : nullptr,
+                                                                       experts, weights, (const bf16*)h, h_stride);
     return ti_check_launch("moe_grouped");
 }

@@ -5,6 +5,13 @@
 //    sigmoid of their logits as weights (or, `softmax`, their share of the softmax over all
 //    experts, not renormalised); one more column of the same product, if there is one,
 //    becomes the sigmoid gate of a shared expert.
+//  * router_choose: scores s = softmax over all outputs of the router; the choice looks at s + correction,
+//    only inside the `keep` groups (of `groups` equal runs of neighbours) whose largest such value is
+//    largest, and takes the `top` largest there (ties: the lower index); the weights are the chosen
+//    outputs' s, as they are.
+//  An index at or behind the number of stacked experts names an *identity expert*: it has no tensors, and
+//  its output is the token's input times the weight.  The kernels below skip its products and add
+//  `w h[t]` where the slots are summed.
 //  * moe_gate_up_simple: y[t][s] = silu(w g) * (w u) with g = Wgate_e h_t, u = Wup_e h_t, e and w
 //    the expert and weight of the token's slot s (an expert's gate and up rows are stacked in one
 //    matrix, interleaved in strips of 8 or one after the other).  The weight stands for a scaling of the
@@ -132,6 +139,70 @@ router_topk_kernel(const float* logits, int stride, int num_tokens, int experts,
     if (shared_col >= 0 && lane == 0) shared_gate[t] = sigmoidf_(z[shared_col]);
 }
 
+constexpr int MAX_ROUTED = 512;       // router outputs a warp keeps in shared memory
+constexpr int MAX_GROUPS = 64;
+
+__global__ void __launch_bounds__(WARPS * 32)
+router_choose_kernel(const float* logits, int stride, int num_tokens, int total, int top,
+                     const float* __restrict__ correction, int groups, int keep,
+                     int* __restrict__ ids, float* __restrict__ weights) {
+    __shared__ float choice[WARPS][MAX_ROUTED];
+    __shared__ float group_best[WARPS][MAX_GROUPS];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * WARPS + warp;
+    if (t >= num_tokens) return;
+    const float* z = logits + (size_t)t * stride;
+    float m = -INFINITY;
+    for (int e = lane; e < total; e += 32) m = fmaxf(m, z[e]);
+    const float z_max = warp_max(m);
+    float acc = 0.0f;
+    for (int e = lane; e < total; e += 32) acc += expf(z[e] - z_max);
+    const float z_sum = warp_sum(acc);
+    float* c = choice[warp];
+    for (int e = lane; e < total; e += 32) c[e] = expf(z[e] - z_max) / z_sum + (correction ? correction[e] : 0.0f);
+    __syncwarp();
+    if (groups > 1 && keep < groups) {
+        const int per = total / groups;
+        float* gb = group_best[warp];
+        for (int g = lane; g < groups; g += 32) {
+            float b = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, c[e]);
+            gb[g] = b;
+        }
+        __syncwarp();
+        // a group stays if fewer than `keep` groups come before it (a larger value, or the same and a lower index)
+        for (int g = lane; g < groups; g += 32) {
+            int before = 0;
+            for (int o = 0; o < groups; ++o) before += gb[o] > gb[g] || (gb[o] == gb[g] && o < g);
+            if (before >= keep)
+                for (int e = g * per; e < (g + 1) * per; ++e) c[e] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    for (int s = 0; s < top; ++s) {
+        float best = -INFINITY;
+        int best_e = total;                           // larger than every index: loses every tie
+        for (int e = lane; e < total; e += 32) {
+            const float v = c[e];
+            if (v > best || (best_e == total && v > -INFINITY)) { best = v; best_e = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (oe < total && (best_e == total || ov > best || (ov == best && oe < best_e))) { best = ov; best_e = oe; }
+        }
+        best_e = __shfl_sync(0xffffffffu, best_e, 0);
+        if (lane == 0) {
+            // fewer outputs left than slots (a configuration the caller refuses): the slot gets weight 0
+            ids[(size_t)t * top + s] = best_e < total ? best_e : 0;
+            weights[(size_t)t * top + s] = best_e < total ? expf(z[best_e] - z_max) / z_sum : 0.0f;
+            if (best_e < total) c[best_e] = -INFINITY;
+        }
+        __syncwarp();
+    }
+}
+
 // one warp per output element f of one (token, slot)
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(WARPS * 32)
@@ -140,7 +211,7 @@ moe_gate_up_simple_kernel(const TA* __restrict__ h, int h_stride, const TW* __re
                           const float* __restrict__ weights, int top, int width, int ff,
                           TA* __restrict__ y, int n_pairs, const TW* __restrict__ shared_gate_up,
                           int shared_interleaved, int shared_ff, TA* __restrict__ y_shared,
-                          int act, float act_limit, float act_alpha) {
+                          int act, float act_limit, float act_alpha, int experts) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int ts = blockIdx.x;                              // token * top + slot; behind the pairs: a token's shared expert
     const int f = blockIdx.y * WARPS + warp;
@@ -154,6 +225,7 @@ moe_gate_up_simple_kernel(const TA* __restrict__ h, int h_stride, const TW* __re
     }
     if (f >= ff) return;
     const int e = shared ? 0 : ids[ts];
+    if (e >= experts) return;                         // an identity expert: nothing to multiply
     const float w = shared ? 1.0f : weights[ts];
     const TA* x = h + (size_t)(shared ? ts : ts / top) * h_stride;
     // an expert's 2 ff rows: strips of 8 gate rows and their 8 up rows, or all gate rows and then all up rows
@@ -179,7 +251,8 @@ moe_down_simple_kernel(const TA* __restrict__ y, const TW* __restrict__ w_down,
                        const int* __restrict__ ids, int top, int width, int ff,
                        float* __restrict__ out, int out_stride, const TA* __restrict__ y_shared,
                        const TW* __restrict__ w_shared_down, const float* __restrict__ shared_gate,
-                       int shared_ff) {
+                       int shared_ff, int experts, const TA* __restrict__ h, int h_stride,
+                       const float* __restrict__ weights) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
     const int n = blockIdx.y * WARPS + warp;
@@ -187,6 +260,10 @@ moe_down_simple_kernel(const TA* __restrict__ y, const TW* __restrict__ w_down,
     float total = 0.0f;
     for (int s = 0; s < top; ++s) {
         const int e = ids[(size_t)t * top + s];
+        if (e >= experts) {                           // an identity expert: the token's input times the weight
+            total = fmaf(weights[(size_t)t * top + s], to_f32(h[(size_t)t * h_stride + n]), total);
+            continue;
+        }
         const TA* ys = y + ((size_t)t * top + s) * ff;
         const TW* wd = w_down + ((size_t)e * width + n) * ff;
         float acc, unused;
@@ -233,12 +310,28 @@ extern "C" int ti_router_topk(const float* logits, int stride, int num_tokens, i
     return ti_check_launch("router_topk");
 }
 
+// `total` router outputs in `groups` equal groups of which `keep` may be chosen from (groups = 1: no groups);
+// `correction` (may be null) is added to the scores for the choice alone.
+extern "C" int ti_router_choose(const float* logits, int stride, int num_tokens, int total, int top,
+                                const float* correction, int groups, int keep, int* ids, float* weights,
+                                void* stream) {
+    if (num_tokens == 0) return 0;
+    TI_REQUIRE(total >= 1 && total <= MAX_ROUTED, "router_choose: %d router outputs (at most %d)", total, MAX_ROUTED);
+    TI_REQUIRE(groups >= 1 && groups <= MAX_GROUPS && total % groups == 0 && keep >= 1 && keep <= groups,
+               "router_choose: %d outputs in %d groups of which %d are kept", total, groups, keep);
+    TI_REQUIRE(top >= 1 && top <= MAX_TOP && top <= total / groups * keep,
+               "router_choose: %d of %d outputs cannot be chosen", top, total / groups * keep);
+    router_choose_kernel<<<(num_tokens + WARPS - 1) / WARPS, WARPS * 32, 0, (cudaStream_t)stream>>>(
+        logits, stride, num_tokens, total, top, correction, groups, keep, ids, weights);
+    return ti_check_launch("router_choose");
+}
+
 extern "C" int ti_moe_gate_up_simple(const void* h, int act_dtype, int h_stride, const void* w_gate_up,
                                      int interleaved, int w_dtype, const int* ids,
                                      const float* weights, int num_tokens, int top, int width, int ff,
                                      void* y, const void* shared_gate_up, int shared_interleaved,
                                      int shared_ff, void* y_shared, int act, float act_limit,
-                                     float act_alpha, void* stream) {
+                                     float act_alpha, int experts, void* stream) {
     if (num_tokens == 0) return 0;
     // with a shared expert (same weight dtype): one more "pair" per token behind the routed ones
     const bool shared = shared_gate_up != nullptr;
@@ -249,7 +342,7 @@ extern "C" int ti_moe_gate_up_simple(const void* h, int act_dtype, int h_stride,
     moe_gate_up_simple_kernel<TA, TW><<<grid, WARPS * 32, 0, s>>>(                            \
         (const TA*)h, h_stride, (const TW*)w_gate_up, interleaved, ids, weights, top, width, ff, (TA*)y, \
         num_tokens * top, (const TW*)shared_gate_up, shared_interleaved, shared_ff, (TA*)y_shared, \
-        act, act_limit, act_alpha)
+        act, act_limit, act_alpha, experts)
     TI_DISPATCH_AW(act_dtype, w_dtype, CALL)
 #undef CALL
     return ti_check_launch("moe_gate_up_simple");
@@ -259,6 +352,7 @@ extern "C" int ti_moe_down_simple(const void* y, int act_dtype, const void* w_do
                                   const int* ids, int num_tokens, int top, int width, int ff,
                                   float* out, int out_stride, const void* y_shared,
                                   const void* w_shared_down, const float* shared_gate, int shared_ff,
+                                  int experts, const void* h, int h_stride, const float* weights,
                                   void* stream) {
     if (num_tokens == 0) return 0;
     dim3 grid(num_tokens, (width + WARPS - 1) / WARPS);
@@ -266,7 +360,7 @@ extern "C" int ti_moe_down_simple(const void* y, int act_dtype, const void* w_do
 #define CALL(TA, TW)                                                                         \
     moe_down_simple_kernel<TA, TW><<<grid, WARPS * 32, 0, s>>>(                               \
         (const TA*)y, (const TW*)w_down, ids, top, width, ff, out, out_stride, (const TA*)y_shared, \
-        (const TW*)w_shared_down, shared_gate, shared_ff)
+        (const TW*)w_shared_down, shared_gate, shared_ff, experts, (const TA*)h, h_stride, weights)
     TI_DISPATCH_AW(act_dtype, w_dtype, CALL)
 #undef CALL
     return ti_check_launch("moe_down_simple");

@@ -13,6 +13,10 @@
 //    gathered rows) or added to a float32 residual.
 //  * depth_mix: hist[index] = x, and, with weights, x = sum_{j <= index} w[j] hist[j].
 //  * add_scaled: dst += sa a + sb b.
+//  * tanh_norm_rows: the norm without a mean or a variance, y = tanh(alpha x) w + b with one scalar alpha;
+//    stored (optionally for gathered rows) or added to a float32 residual, like the norm in groups.
+//  * cap_rows: x = cap tanh(x / cap), in place.
+//  * add_row: x[t] += row for every row of x.
 //  * glu_rows: y = act(gate, up) over a float32 product that holds gate and up columns (stacked, or
 //    in strips of 8 and 8).  GLU_CLAMPED: g = min(g, limit), u = clamp(u, -limit, limit),
 //    y = g sigmoid(alpha g) (u + 1).
@@ -152,6 +156,33 @@ glu_rows_kernel(const float* gu, int inter, size_t total, int interleaved, int k
     out[i] = from_f32<TO>(glu_activation(kind, row[gate_at], row[up_at], limit, alpha));
 }
 
+// y = tanh(alpha x) w + b over rows of n elements: element-wise, so a thread per element
+template <typename TO, bool ADD>
+__global__ void tanh_norm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, int n, size_t total,
+                                      float alpha, const float* __restrict__ w, const float* __restrict__ b,
+                                      TO* __restrict__ out, float* residual, int res_stride) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t r = i / n;
+    const int c = (int)(i % n);
+    const size_t src = rows ? (size_t)rows[r] : r;
+    const float y = fmaf(tanhf(alpha * x[src * n + c]), w[c], b ? b[c] : 0.0f);
+    if constexpr (ADD) residual[r * res_stride + c] += y;
+    else out[i] = from_f32<TO>(y);
+}
+
+__global__ void cap_rows_kernel(float* __restrict__ x, size_t total, float cap) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] = cap * tanhf(x[i] / cap);
+}
+
+__global__ void add_row_kernel(float* __restrict__ x, int stride, const float* __restrict__ row, int cols, size_t total) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int c = (int)(i % cols);
+    x[(i / cols) * stride + c] += row[c];
+}
+
 }  // namespace
 
 extern "C" int ti_causal_conv_rows(const float* x, int x_stride, const float* w, int taps, int channels, int rows,
@@ -236,4 +267,37 @@ extern "C" int ti_glu_rows(const float* gu, int num_tokens, int inter, int inter
         glu_rows_kernel<float><<<blocks, 256, 0, s>>>(gu, inter, total, interleaved, kind, limit, alpha, (float*)out);
     else return ti_fail("glu_rows: output dtype code %d", out_dtype);
     return ti_check_launch("glu_rows");
+}
+
+extern "C" int ti_tanh_norm_rows(const float* x, const int* rows, int num_rows, int n, float alpha, const float* w,
+                                 const float* b, void* out, int out_dtype, float* residual, int res_stride, void* stream) {
+    const size_t total = (size_t)num_rows * n;
+    if (total == 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (residual != nullptr) {
+        TI_REQUIRE(rows == nullptr, "tanh_norm_rows: rows are not gathered when adding to a residual");
+        tanh_norm_rows_kernel<float, true><<<blocks, 256, 0, s>>>(x, rows, n, total, alpha, w, b, nullptr, residual, res_stride);
+    } else if (out_dtype == TI_BF16) {
+        tanh_norm_rows_kernel<bf16, false><<<blocks, 256, 0, s>>>(x, rows, n, total, alpha, w, b, (bf16*)out, nullptr, 0);
+    } else if (out_dtype == TI_F32) {
+        tanh_norm_rows_kernel<float, false><<<blocks, 256, 0, s>>>(x, rows, n, total, alpha, w, b, (float*)out, nullptr, 0);
+    } else {
+        return ti_fail("tanh_norm_rows: output dtype code %d", out_dtype);
+    }
+    return ti_check_launch("tanh_norm_rows");
+}
+
+extern "C" int ti_cap_rows(float* x, long long total, float cap, void* stream) {
+    if (total == 0) return 0;
+    TI_REQUIRE(cap > 0.0f, "cap_rows: the cap must be positive");
+    cap_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, (size_t)total, cap);
+    return ti_check_launch("cap_rows");
+}
+
+extern "C" int ti_add_row(float* x, int stride, const float* row, int rows, int cols, void* stream) {
+    const size_t total = (size_t)rows * cols;
+    if (total == 0) return 0;
+    add_row_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, stride, row, cols, total);
+    return ti_check_launch("add_row");
 }

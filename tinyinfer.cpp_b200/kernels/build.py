@@ -32,8 +32,10 @@ LIBRARIES = {
     # attention with optional parts (chunks, caps, sinks, gates, shared rows) and the recurrent mixer
     "mixers": ["common.cu", "attn_options.cu", "wkv.cu"],
     "bf16_mixers": ["common.cu", "attn_options_tc.cu"],
-    # recurrent mixers with a matrix state, short convolutions over time, norms in groups
-    "state": ["common.cu", "matrix_state.cu", "state_rows.cu"],
+    # recurrent mixers with a matrix state
+    "state": ["common.cu", "matrix_state.cu"],
+    # short convolutions over time, norms in groups and without statistics, depth sums, gated activations
+    "rows": ["common.cu", "state_rows.cu"],
 }
 
 # libraries that parts bring themselves: name -> (absolute source paths, include folders)

@@ -213,9 +213,11 @@ class CudaOps(MixerOps, StateOps):
         c.ti_attention_bias_simple.argtypes = [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
                                                _i, _i, _i, _i, _f, _vp, _i, _vp, _i, _vp, _vp, _vp]
         c.ti_router_topk.argtypes = [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp]
+        c.ti_router_choose.argtypes = [_vp, _i, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp]
         c.ti_moe_gate_up_simple.argtypes = [_vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _i,
-                                            _vp, _i, _f, _f, _vp]
-        c.ti_moe_down_simple.argtypes = [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _i, _vp]
+                                            _vp, _i, _f, _f, _i, _vp]
+        c.ti_moe_down_simple.argtypes = [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp,
+                                         _i, _vp, _vp]
         c.ti_scale_rows.argtypes = [_vp, _i, _i, _vp, _i, _i, _vp]
 
     @property
@@ -292,10 +294,10 @@ class CudaOps(MixerOps, StateOps):
                                               _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp]
             b.ti_moe_grouped_supported.argtypes = [_i, _i, _i]
             b.ti_moe_grouped.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp,
-                                         _vp, _vp, _i, _i, _f, _f, _vp]
+                                         _vp, _vp, _i, _i, _f, _f, _i, _vp]
             b.ti_moe_sort_padded.argtypes = [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]
             b.ti_moe_gather_scaled.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp]
-            b.ti_moe_combine_rows.argtypes = [_vp, _vp, _i, _i, _i, _vp, _i, _vp, _vp]
+            b.ti_moe_combine_rows.argtypes = [_vp, _vp, _i, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _i, _vp]
             self._gated = b
         return self._gated
 
@@ -652,6 +654,8 @@ class CudaOps(MixerOps, StateOps):
         self._rotations[kind] = handler
 
     def _rotation_handler(self, rotation):
+        _need(getattr(rotation, "scale", 1.0) == 1.0,
+              "these kernels turn heads without a factor on sine and cosine (rotation.scale must be 1)")
         try:
             return self._rotations[rotation.kind]
         except KeyError:
@@ -899,14 +903,14 @@ class CudaOps(MixerOps, StateOps):
     # ---- attention with a distance bias, kept first tokens and an output gate ---------------
     def embed_sinusoid(self, table, token_ids, positions, freq, scale, out):
         """out[t] = float32(table[token_ids[t]]) * scale + wave(positions[t]); wave(p)[2i] =
-        sin(p freq[i]), wave(p)[2i + 1] = cos(p freq[i])."""
+        sin(p freq[i]), wave(p)[2i + 1] = cos(p freq[i]); ``freq`` None: no wave."""
         _need(out.dtype == torch.float32 and out.is_contiguous(), "embed_sinusoid: out must be float32")
         _need(token_ids.dtype == torch.int32 and positions.dtype == torch.int32,
               "embed_sinusoid: token ids and positions must be int32")
-        _need(freq.dtype == torch.float32 and freq.shape[0] >= (table.shape[1] + 1) // 2,
+        _need(freq is None or (freq.dtype == torch.float32 and freq.shape[0] >= (table.shape[1] + 1) // 2),
               "embed_sinusoid: one float32 frequency per pair of columns")
         self._ok(self.core.ti_embed_sinusoid(table.data_ptr(), _code(table, "embed_sinusoid"),
-                                             token_ids.data_ptr(), positions.data_ptr(), freq.data_ptr(),
+                                             token_ids.data_ptr(), positions.data_ptr(), _ptr(freq),
                                              float(scale), token_ids.shape[0], table.shape[1],
                                              out.data_ptr(), self._stream()))
 
@@ -1077,15 +1081,35 @@ class CudaOps(MixerOps, StateOps):
                                           weights.data_ptr(), _ptr(shared_gate), int(bool(softmax)),
                                           self._stream()))
 
-    def routed_experts(self, h, w, ids, weights, residual, shared=None, act=None):
+    def router_choose(self, logits, total, top, ids, weights, correction=None, groups=1, keep=1):
+        """Per row, from the first ``total`` float32 logits: scores ``s = softmax(logits)``; the
+        choice looks at ``s + correction`` (float32 ``[total]`` or None), only inside the ``keep`` of
+        ``groups`` equal groups of neighbouring outputs whose largest such value is largest, and
+        takes the ``top`` largest there (ties: the lower index).  ``ids`` int32 and ``weights``
+        float32 ``[rows, top]``: the chosen outputs and their ``s``, not renormalised."""
+        t = logits.shape[0]
+        _need(logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[1] >= total,
+              "router_choose: float32 logits")
+        _need(correction is None or (correction.dtype == torch.float32 and correction.is_contiguous()
+                                     and correction.shape[0] == total), "router_choose: one float32 correction per output")
+        _need(ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.is_contiguous()
+              and weights.is_contiguous() and tuple(ids.shape) == tuple(weights.shape) == (t, top),
+              "router_choose: ids int32 and weights float32, [rows, top]")
+        self._ok(self.core.ti_router_choose(logits.data_ptr(), logits.stride(0), t, int(total), int(top),
+                                            _ptr(correction), int(groups), int(keep), ids.data_ptr(),
+                                            weights.data_ptr(), self._stream()))
+
+    def routed_experts(self, h, w, ids, weights, residual, shared=None, act=None, identity=False):
         """residual[t] += sum over slots s of Wdown_e (silu(w g) * (w u)), g = Wgate_e h[t],
         u = Wup_e h[t], e = ids[t, s], w = weights[t, s].  ``shared`` (may be None):
         ``(w_gate_up from pack_gate_up, w_down, gate)`` of an expert that every token uses, its
         output times ``gate[t]``: residual[t] += gate[t] * Wdown (silu(g) * u).  Few tokens run
         it inside the experts' two launches.  ``act`` (may be None: silu) names another gated
         activation, ``(kind, limit, alpha)`` as ``glu_rows`` takes them; the pair's weight then
-        scales the expert's output, residual[t] += w Wdown_e act(g, u), and there is no ``shared``."""
-        self._routed(h, w, ids, weights, residual, shared, act)
+        scales the expert's output, residual[t] += w Wdown_e act(g, u), and there is no ``shared``.
+        ``identity``: an index at or behind the number of stacked experts names an identity expert,
+        whose output is the token's input, residual[t] += w h[t]."""
+        self._routed(h, w, ids, weights, residual, shared, act, identity)
 
     def _shared_expert(self, h, shared, residual):
         w_gate_up, w_down, gate = shared
@@ -1094,7 +1118,7 @@ class CudaOps(MixerOps, StateOps):
         self.scale_rows(y, gate)
         self.linear(y, w_down, residual, accumulate=True)
 
-    def _routed(self, h, w, ids, weights, residual, shared, act=None):
+    def _routed(self, h, w, ids, weights, residual, shared, act=None, identity=False):
         from .state_ops import GLU_KINDS
         act_kind, act_limit, act_alpha = (0, 0.0, 0.0) if act is None else (GLU_KINDS[act[0]], float(act[1]), float(act[2]))
         _need(act_kind == 0 or shared is None, "routed_experts: a shared expert rides only with the silu activation")
@@ -1142,7 +1166,9 @@ class CudaOps(MixerOps, StateOps):
                     self._stream()), self.bf16)
                 self._ok(g.ti_moe_combine_rows(out_rows.data_ptr(), pos_of_pair.data_ptr(), top, width, t,
                                                residual.data_ptr(), residual.stride(0),
-                                               None if act_kind == 0 else weights.data_ptr(), self._stream()), g)
+                                               None if act_kind == 0 else weights.data_ptr(),
+                                               ids.data_ptr() if identity else None, experts, weights.data_ptr(),
+                                               h.data_ptr(), h.stride(0), self._stream()), g)
                 if shared is not None:
                     self._shared_expert(h, shared, residual)
                 return
@@ -1154,7 +1180,7 @@ class CudaOps(MixerOps, StateOps):
                 ids.data_ptr(), weights.data_ptr(), t, top, experts, width, ff, ints.data_ptr(),
                 ints[pairs:].data_ptr(), ints[ints.shape[0] - 1:].data_ptr(), y_sorted.data_ptr(),
                 out_rows.data_ptr(), residual.data_ptr(), residual.stride(0), act_kind, act_limit, act_alpha,
-                self._stream()), self.gated)
+                int(bool(identity)), self._stream()), self.gated)
             self.launches += 3
             if shared is not None:
                 self._shared_expert(h, shared, residual)
@@ -1178,11 +1204,13 @@ class CudaOps(MixerOps, StateOps):
         self._ok(self.core.ti_moe_gate_up_simple(
             h.data_ptr(), _code(h, "routed_experts"), h.stride(0), gate_up.data_ptr(), interleaved,
             _code(gate_up, "routed_experts"), ids.data_ptr(), weights.data_ptr(), t, top, width, ff,
-            y.data_ptr(), _ptr(sgu), s_inter, s_ff, _ptr(y_sh), act_kind, act_limit, act_alpha, self._stream()))
+            y.data_ptr(), _ptr(sgu), s_inter, s_ff, _ptr(y_sh), act_kind, act_limit, act_alpha,
+            experts if identity else 1 << 30, self._stream()))
         self._ok(self.core.ti_moe_down_simple(
             y.data_ptr(), _code(y, "routed_experts"), w["down"].data_ptr(), _code(w["down"], "routed_experts"),
             ids.data_ptr(), t, top, width, ff, residual.data_ptr(), residual.stride(0), _ptr(y_sh), _ptr(sdown),
-            _ptr(sgate), s_ff, self._stream()))
+            _ptr(sgate), s_ff, experts if identity else 1 << 30, h.data_ptr(), h.stride(0), weights.data_ptr(),
+            self._stream()))
         if shared is not None and not ride:
             self._shared_expert(h, shared, residual)
 

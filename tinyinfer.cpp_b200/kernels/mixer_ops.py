@@ -10,6 +10,10 @@ qk_rownorm_rope_store(proj, ...)     norm over the whole query row and the whole
                                      of neighbouring pairs, keys/values into pages, queries out
 latent_prepare(proj, ...)            normed latent + turned key part as one cached row; plain
                                      and turned query parts out
+qkv_turn_store(proj, ...)            no norm: queries and keys turned, values turned by frequencies of
+                                     their own, keys/values into pages, queries out
+turn_rows(x, step, rotation, ...)    finished rows' heads turned by plus or minus their position, times
+                                     sigmoid(gate)
 head_project(x, w, out)              out[t, h] = x[t, h] @ w[h]
 attention_options(q, step, cache, out, ...)
 token_shift_mix(h, mu, step, state, out)
@@ -78,8 +82,11 @@ class MixerOps:
             b.ti_last_error.restype = ctypes.c_char_p
             b.ti_qk_rownorm_rope_store.argtypes = [_vp, _i, _vp, _vp, _f, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i,
                                                    _i, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp]
-            b.ti_latent_prepare.argtypes = [_vp, _i, _vp, _f, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
-                                            _i, _i, _vp, _vp, _i, _vp, _vp]
+            b.ti_latent_prepare.argtypes = [_vp, _i, _vp, _i, _vp, _f, _vp, _f, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i,
+                                            _i, _i, _i, _vp, _vp, _i, _vp, _vp]
+            b.ti_qkv_turn_store.argtypes = [_vp, _i, _vp, _i, _i, _f, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i,
+                                            _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp]
+            b.ti_turn_rows.argtypes = [_vp, _i, _vp, _vp, _i, _i, _f, _vp, _i, _i, _i, _i, _vp, _vp]
             b.ti_head_project.argtypes = [_vp, _i, _i, _i, _vp, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _vp]
             b.ti_attention_options.argtypes = [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
                                                _i, _i, _i, _f, _f, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp]
@@ -116,6 +123,7 @@ class MixerOps:
         self._must(rotation.kind in ("interleaved", "none"),
                    f"qk_rownorm_rope_store turns neighbouring pairs; rotation kind {rotation.kind!r} is not that")
         rot = int(rotation.rotary_dim)
+        self._must(getattr(rotation, "scale", 1.0) == 1.0, "qk_rownorm_rope_store: a pure turn only (no factor on sine and cosine)")
         self._must(proj.dtype == torch.float32 and proj.stride(1) == 1
                    and proj.shape[1] >= nq + (nk + nv if cache.writes else 0),
                    "qk_rownorm_rope_store: the product must be float32 and hold all heads")
@@ -137,19 +145,25 @@ class MixerOps:
             _CODE[q_out.dtype], self.status.data_ptr(), self._stream()))
 
     def latent_prepare(self, proj, latent_weight, eps, rotation, step, cache, q_plain, q_full,
-                       num_heads, dk, dr, rank):
+                       num_heads, dk, dr, rank, q_proj=None):
         """From the float32 product ``proj`` (columns: per head ``dk`` plain and ``dr`` rotated
         query elements, then the latent of ``rank`` elements and one rotated key part of ``dr``):
         the latent, normed (weight or None), and the turned key part go into the token's page as one
         row of ``rank + dr``; ``q_plain`` ``[T, heads * dk]`` gets the plain query parts and
-        ``q_full[:, h, rank:]`` (``[T, heads, rank + dr]``) the turned ones."""
+        ``q_full[:, h, rank:]`` (``[T, heads, rank + dr]``) the turned ones.  With ``q_proj`` the
+        query heads are its columns and ``proj`` starts with the latent.  The sines and cosines of
+        both turned parts are multiplied by ``rotation.scale``."""
         t = proj.shape[0]
         pages, bt = cache.pages, cache.block_table
+        nq = num_heads * (dk + dr)
         self._must(dr == 0 or (rotation.kind == "interleaved" and rotation.rotary_dim == dr),
                    "latent_prepare turns the whole rotated part in neighbouring pairs")
-        self._must(proj.dtype == torch.float32 and proj.stride(1) == 1
-                   and proj.shape[1] >= num_heads * (dk + dr) + rank + dr,
-                   "latent_prepare: the product must be float32 and hold queries, latent and key part")
+        if q_proj is None:
+            q_proj, proj = proj, proj[:, nq:]
+        self._must(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= rank + dr
+                   and q_proj.dtype == torch.float32 and q_proj.stride(1) == 1 and q_proj.shape[1] >= nq
+                   and q_proj.shape[0] == t,
+                   "latent_prepare: the products must be float32 and hold queries, latent and key part")
         self._must(latent_weight is None or (latent_weight.dtype == torch.float32 and latent_weight.shape[0] == rank),
                    "latent_prepare: the latent's norm weight must be float32")
         self._must(pages.is_contiguous() and pages[0].numel() == cache.page_size * (rank + dr),
@@ -160,11 +174,67 @@ class MixerOps:
                    and q_full.numel() == t * num_heads * (rank + dr), "latent_prepare: query outputs")
         self._must(bool(cache.writes), "latent_prepare writes the cache slot")
         self._mx(self.mixers.ti_latent_prepare(
-            proj.data_ptr(), proj.stride(0), _ptr(latent_weight), float(eps),
-            _ptr(rotation.inv_freq) if dr else None, step.positions.data_ptr(), step.req_of_tok.data_ptr(),
+            q_proj.data_ptr(), q_proj.stride(0), proj.data_ptr(), proj.stride(0), _ptr(latent_weight), float(eps),
+            _ptr(rotation.inv_freq) if dr else None, float(getattr(rotation, "scale", 1.0)),
+            step.positions.data_ptr(), step.req_of_tok.data_ptr(),
             bt.data_ptr(), bt.stride(0), pages.data_ptr(), _CODE[pages.dtype], pages.shape[0], cache.page_size,
             t, num_heads, dk, dr, rank, q_plain.data_ptr(), q_full.data_ptr(), _CODE[q_plain.dtype],
             self.status.data_ptr(), self._stream()))
+
+    _LAYOUTS = {"interleaved": 0, "neox": 1}
+
+    def qkv_turn_store(self, proj, rotation, v_rotation, step, cache, q_out, num_heads, num_kv_heads, dk, dv):
+        """From the float32 rows ``proj`` (columns: queries, keys, values): no norm; the first
+        ``rotation.rotary_dim`` elements of every query and key head are turned by the token's
+        position (kind ``interleaved``: neighbouring pairs; ``neox``: element ``i`` with ``i +
+        rotary_dim / 2``; ``none``), the first ``v_rotation.rotary_dim`` elements of every value
+        head by ``v_rotation`` (or None: values as they are); keys and values go into the token's
+        page (if the cache slot is written), queries into ``q_out``."""
+        t = proj.shape[0]
+        pages, bt = cache.pages, cache.block_table
+        nq, nk, nv = num_heads * dk, num_kv_heads * dk, num_kv_heads * dv
+        rots = []
+        for what, r, size in (("heads", rotation, dk), ("values", v_rotation, dv)):
+            n = 0 if r is None or r.kind == "none" else int(r.rotary_dim)
+            self._must(n == 0 or (r.kind in self._LAYOUTS and r.inv_freq is not None and r.inv_freq.dtype == torch.float32
+                                  and r.inv_freq.shape[0] >= n // 2 and n <= size),
+                       f"qkv_turn_store: the rotation of the {what} needs a known pairing and rotary_dim/2 float32 frequencies")
+            rots.append((n, self._LAYOUTS.get(r.kind, 0) if n else 0, _ptr(r.inv_freq) if n else None,
+                         float(getattr(r, "scale", 1.0)) if n else 1.0))
+        self._must(rots[1][3] == 1.0, "qkv_turn_store: values are turned without a factor")
+        self._must(proj.dtype == torch.float32 and proj.stride(1) == 1
+                   and proj.shape[1] >= nq + (nk + nv if cache.writes else 0),
+                   "qkv_turn_store: the rows must be float32 and hold all heads")
+        self._must(pages.is_contiguous() and pages[0].numel() == num_kv_heads * cache.page_size * (dk + dv),
+                   "qkv_turn_store: page layout")
+        self._must(bt.dtype == torch.int32 and bt.stride(1) == 1, "qkv_turn_store: block table int32")
+        self._must(q_out.is_contiguous() and tuple(q_out.shape) == (t, nq), "qkv_turn_store: q_out")
+        self._mx(self.mixers.ti_qkv_turn_store(
+            proj.data_ptr(), proj.stride(0), rots[0][2], rots[0][0], rots[0][1], rots[0][3], rots[1][2], rots[1][0],
+            rots[1][1], step.positions.data_ptr(), step.req_of_tok.data_ptr(), bt.data_ptr(), bt.stride(0),
+            pages.data_ptr(), _CODE[pages.dtype], pages.shape[0], cache.page_size, int(bool(cache.writes)), t,
+            num_heads, num_kv_heads, dk, dv, q_out.data_ptr(), _CODE[q_out.dtype], self.status.data_ptr(),
+            self._stream()))
+
+    def turn_rows(self, x, step, rotation, num_heads, n, back=False, gate=None, out=None):
+        """``out[t, h, :]`` is head ``h`` of row ``t`` of ``x`` (``[T, heads * n]``) with its first
+        ``rotation.rotary_dim`` elements turned by the token's position, or, ``back``, by minus the
+        position; then times ``sigmoid(gate)`` (float32 ``[T, heads * n]``) if given.  ``out`` None:
+        in place."""
+        t = x.shape[0]
+        out = x if out is None else out
+        rot = 0 if rotation is None or rotation.kind == "none" else int(rotation.rotary_dim)
+        self._must(x.is_contiguous() and out.is_contiguous() and x.dtype == out.dtype
+                   and tuple(x.shape) == tuple(out.shape) == (t, num_heads * n), "turn_rows: contiguous [T, heads * n] rows")
+        self._must(rot == 0 or (rotation.kind in self._LAYOUTS and rotation.inv_freq is not None
+                                and rotation.inv_freq.dtype == torch.float32 and rotation.inv_freq.shape[0] >= rot // 2),
+                   "turn_rows: the rotation needs a known pairing and rotary_dim/2 float32 frequencies")
+        self._must(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1
+                                    and tuple(gate.shape) == (t, num_heads * n)), "turn_rows: a float32 gate per element")
+        self._mx(self.mixers.ti_turn_rows(
+            x.data_ptr(), _CODE[x.dtype], step.positions.data_ptr(), _ptr(rotation.inv_freq) if rot else None, rot,
+            self._LAYOUTS.get(rotation.kind, 0) if rot else 0, -1.0 if back else 1.0, _ptr(gate),
+            gate.stride(0) if gate is not None else 0, t, num_heads, n, out.data_ptr(), self._stream()))
 
     def head_project(self, x, w, out):
         """``out[t, h, :] = x[t, h, :] @ w[h]`` for ``x [T, heads, n_in]``, ``w [heads, n_in, n_out]``

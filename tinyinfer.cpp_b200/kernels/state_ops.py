@@ -1,14 +1,17 @@
-"""Bindings of the kernels in ``csrc/matrix_state.cu`` and ``csrc/state_rows.cu`` (library
-``state``): recurrent mixers with a float32 matrix state per head, short causal convolutions
+"""Bindings of the kernels in ``csrc/matrix_state.cu`` (library ``state``) and
+``csrc/state_rows.cu`` (library ``rows``): recurrent mixers with a float32 matrix state per head, short causal convolutions
 over time with their kept inputs, norms in groups, the depth-weighted mix of layer outputs, and
 gated activations with clamps.
 
-``CudaOps`` inherits these methods; the library is built when one of them is first called, so
-a model without such parts never compiles it.
+``CudaOps`` inherits these methods; each library is built when one of its kernels is first called, so
+a model without a recurrence never compiles ``state``, and one without any of these parts neither.
 
 causal_conv(x, w, step, state, offset, out, add_input, silu)   y = [x +] conv(x) [silu], rows before a portion from the state
 conv_tail_store(x, taps, step, state, offset)                  the state's kept inputs renewed after a step
 group_norm(x, w, eps, groups, out | residual, rows)            RMS norm in equal consecutive parts of a row
+tanh_norm(x, alpha, w, b, out | residual, rows)                tanh(alpha x) w + b, the norm without mean or variance
+cap_rows(x, cap)                                               x = cap tanh(x / cap), in place
+add_row(x, row)                                                x[t] += row
 depth_mix(x, hist, index, weights)                             hist[index] = x; x = sum_j weights[j] hist[j]
 add_scaled(dst, a, sa, b, sb)                                  dst += sa a + sb b
 glu_rows(gu, interleaved, kind, limit, alpha, out)             out = act(gate, up)
@@ -43,23 +46,39 @@ class StateOps:
     _state_lib = None
     cut_state_columns = True          # long portions of few requests: a head's columns over several blocks
 
+    _rows_lib = None
+
     @property
     def state_lib(self):
         if self._state_lib is None:
             b = load_library("state")
             b.ti_last_error.restype = ctypes.c_char_p
-            b.ti_causal_conv_rows.argtypes = [_vp, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _vp,
-                                              _i, _i, _vp]
-            b.ti_conv_tail_store.argtypes = [_vp, _i, _i, _i, _vp, _vp, _i, _vp, _ll, _ll, _vp]
-            b.ti_group_norm_rows.argtypes = [_vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _vp, _i, _vp]
-            b.ti_depth_mix.argtypes = [_vp, _vp, _ll, _i, _vp, _vp]
-            b.ti_add_scaled.argtypes = [_vp, _i, _vp, _f, _vp, _f, _i, _i, _vp]
-            b.ti_glu_rows.argtypes = [_vp, _i, _i, _i, _i, _f, _f, _vp, _i, _vp]
             b.ti_matrix_state.argtypes = [_i, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _f, _vp, _i, _i,
                                           _vp, _i, _f, _vp, _vp, _i, _i, _vp, _ll, _i, _i, _i, _i, _i, _vp, _i, _vp,
                                           _vp, _vp]
             self._state_lib = b
         return self._state_lib
+
+    @property
+    def rows_lib(self):
+        if self._rows_lib is None:
+            b = load_library("rows")
+            b.ti_last_error.restype = ctypes.c_char_p
+            b.ti_causal_conv_rows.argtypes = [_vp, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _vp,
+                                              _i, _i, _vp]
+            b.ti_conv_tail_store.argtypes = [_vp, _i, _i, _i, _vp, _vp, _i, _vp, _ll, _ll, _vp]
+            b.ti_group_norm_rows.argtypes = [_vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _vp, _i, _vp]
+            b.ti_tanh_norm_rows.argtypes = [_vp, _vp, _i, _i, _f, _vp, _vp, _vp, _i, _vp, _i, _vp]
+            b.ti_cap_rows.argtypes = [_vp, _ll, _f, _vp]
+            b.ti_add_row.argtypes = [_vp, _i, _vp, _i, _i, _vp]
+            b.ti_depth_mix.argtypes = [_vp, _vp, _ll, _i, _vp, _vp]
+            b.ti_add_scaled.argtypes = [_vp, _i, _vp, _f, _vp, _f, _i, _i, _vp]
+            b.ti_glu_rows.argtypes = [_vp, _i, _i, _i, _i, _f, _f, _vp, _i, _vp]
+            self._rows_lib = b
+        return self._rows_lib
+
+    def _rw(self, rc: int) -> None:
+        self._ok(rc, self.rows_lib)
 
     def _st(self, rc: int) -> None:
         self._ok(rc, self.state_lib)
@@ -90,7 +109,7 @@ class StateOps:
                    "causal_conv: the state must hold taps - 1 float32 rows")
         renew = bool(renew) and taps > 1 and state.writes
         in_place = renew and step.max_q_len == 1 and step.num_requests == t
-        self._st(self.state_lib.ti_causal_conv_rows(
+        self._rw(self.rows_lib.ti_causal_conv_rows(
             x.data_ptr(), x.stride(0), _ptr(w), taps, c, t, step.req_of_tok.data_ptr(), step.cu_q.data_ptr(),
             _ptr(state.slots) if state is not None else None, _ptr(st), st.stride(0) if st is not None else 0,
             int(state_offset), int(bool(add_input)), int(bool(silu)), int(in_place), out.data_ptr(), _CODE[out.dtype],
@@ -106,7 +125,7 @@ class StateOps:
         c = x.shape[1]
         st = state.state
         self._want(x.dtype == torch.float32 and x.stride(1) == 1, "conv_tail_store: float32 rows")
-        self._st(self.state_lib.ti_conv_tail_store(
+        self._rw(self.rows_lib.ti_conv_tail_store(
             x.data_ptr(), x.stride(0), int(taps), c, step.cu_q.data_ptr(), state.slots.data_ptr(),
             step.num_requests, st.data_ptr(), st.stride(0), int(state_offset), self._stream()))
 
@@ -125,10 +144,43 @@ class StateOps:
                        and tuple(residual.shape) == tuple(x.shape), "group_norm: a float32 residual of x's shape")
         else:
             self._want(out is not None and out.is_contiguous() and tuple(out.shape) == (num, n), "group_norm: out")
-        self._st(self.state_lib.ti_group_norm_rows(
+        self._rw(self.rows_lib.ti_group_norm_rows(
             x.data_ptr(), weight.data_ptr(), _ptr(rows), num, n, int(groups), float(eps), _ptr(out),
             _CODE[out.dtype] if out is not None else 0, _ptr(residual),
             residual.stride(0) if residual is not None else 0, self._stream()))
+
+    def tanh_norm(self, x, alpha, weight, bias, out=None, rows=None, residual=None):
+        """``tanh(alpha x) weight + bias`` for every row of the float32 ``x`` (one scalar ``alpha``, a
+        weight and, if not None, a bias per element): stored in ``out`` (of the rows ``rows`` if given),
+        or added to the float32 ``residual``."""
+        n = x.shape[1]
+        self._want(x.dtype == torch.float32 and x.is_contiguous() and weight.dtype == torch.float32
+                   and weight.is_contiguous() and weight.shape[0] == n
+                   and (bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.shape[0] == n)),
+                   "tanh_norm: float32 rows, a float32 weight and bias per element")
+        num = x.shape[0] if rows is None else rows.shape[0]
+        if residual is not None:
+            self._want(rows is None and residual.dtype == torch.float32 and residual.stride(1) == 1
+                       and tuple(residual.shape) == tuple(x.shape), "tanh_norm: a float32 residual of x's shape")
+        else:
+            self._want(out is not None and out.is_contiguous() and tuple(out.shape) == (num, n)
+                       and (rows is None or rows.dtype == torch.int32), "tanh_norm: out")
+        self._rw(self.rows_lib.ti_tanh_norm_rows(
+            x.data_ptr(), _ptr(rows), num, n, float(alpha), weight.data_ptr(), _ptr(bias), _ptr(out),
+            _CODE[out.dtype] if out is not None else 0, _ptr(residual),
+            residual.stride(0) if residual is not None else 0, self._stream()))
+
+    def cap_rows(self, x, cap):
+        """``x = cap tanh(x / cap)`` over a contiguous float32 tensor, in place."""
+        self._want(x.dtype == torch.float32 and x.is_contiguous(), "cap_rows: contiguous float32")
+        self._rw(self.rows_lib.ti_cap_rows(x.data_ptr(), x.numel(), float(cap), self._stream()))
+
+    def add_row(self, x, row):
+        """``x[t] += row`` for every row of the float32 ``x``."""
+        self._want(x.dtype == torch.float32 and x.stride(1) == 1 and row.dtype == torch.float32 and row.is_contiguous()
+                   and row.numel() == x.shape[1], "add_row: float32 rows and one float32 row of their length")
+        self._rw(self.rows_lib.ti_add_row(x.data_ptr(), x.stride(0), row.data_ptr(), x.shape[0], x.shape[1],
+                                           self._stream()))
 
     def depth_mix(self, x, hist, index, weights=None):
         """``hist[index] = x`` and, with ``weights`` (float32, ``index + 1`` of them),
@@ -139,7 +191,7 @@ class StateOps:
                    "depth_mix: float32 rows and a history of such rows")
         self._want(weights is None or (weights.dtype == torch.float32 and weights.is_contiguous()
                                        and weights.shape[0] == index + 1), "depth_mix: index + 1 float32 weights")
-        self._st(self.state_lib.ti_depth_mix(x.data_ptr(), hist.data_ptr(), x.numel(), int(index), _ptr(weights),
+        self._rw(self.rows_lib.ti_depth_mix(x.data_ptr(), hist.data_ptr(), x.numel(), int(index), _ptr(weights),
                                              self._stream()))
 
     def add_scaled(self, dst, a, sa, b=None, sb=0.0):
@@ -148,7 +200,7 @@ class StateOps:
                    and tuple(a.shape) == tuple(dst.shape)
                    and (b is None or (b.dtype == torch.float32 and b.is_contiguous() and b.shape == a.shape)),
                    "add_scaled: float32 rows of one shape")
-        self._st(self.state_lib.ti_add_scaled(dst.data_ptr(), dst.stride(0), a.data_ptr(), float(sa), _ptr(b), float(sb),
+        self._rw(self.rows_lib.ti_add_scaled(dst.data_ptr(), dst.stride(0), a.data_ptr(), float(sa), _ptr(b), float(sb),
                                               dst.shape[0], dst.shape[1], self._stream()))
 
     def glu_rows(self, gu, interleaved, kind, limit, alpha, out):
@@ -158,7 +210,7 @@ class StateOps:
         t, n = out.shape
         self._want(gu.dtype == torch.float32 and gu.is_contiguous() and tuple(gu.shape) == (t, 2 * n)
                    and out.is_contiguous(), "glu_rows: a float32 product of gate and up columns")
-        self._st(self.state_lib.ti_glu_rows(gu.data_ptr(), t, n, int(bool(interleaved)), GLU_KINDS[kind], float(limit),
+        self._rw(self.rows_lib.ti_glu_rows(gu.data_ptr(), t, n, int(bool(interleaved)), GLU_KINDS[kind], float(limit),
                                             float(alpha), out.data_ptr(), _CODE[out.dtype], self._stream()))
 
     # ---- recurrences over a matrix state -------------------------------------------------------------

@@ -2,7 +2,7 @@
 from .base import (FixedStateSpec, MATRIX, NORM_WEIGHT, PagedKVSpec, Part, WeightSpec, build_part,
                    register_part)
 from . import (norm, rope, attention, gated_attention, chunked_attention, latent_attention, wkv,  # noqa: F401
-               state_mixers, parallel_mixers, mlp, moe, block, embed_head)  # noqa: F401  (register the parts)
+               state_mixers, parallel_mixers, conv_attention, junction, mlp, moe, block, embed_head)  # noqa: F401  (register the parts)
 from .attention import Attention
 from .block import PreNormBlock
 from .embed_head import Embedding, LMHead

@@ -1,7 +1,7 @@
 """Interfaces of the parts a decoder is put together from, and their registry.
 
 Categories: ``norm``, ``position``, ``mixer``, ``ffn``, ``block``, ``embedding``,
-``head``.  A part is built from a ``PartSpec`` (kind + parameters); it declares
+``head``, ``junction``.  A part is built from a ``PartSpec`` (kind + parameters); it declares
 the tensors it needs under names local to itself (``weight_specs``), receives
 them once (``load_weights``), and then runs on device tensors through the
 kernel set ``ops`` that the step hands it.  A part never sees the model's
@@ -17,6 +17,8 @@ mixer     ``cache_spec()``: what it keeps per request (``PagedKVSpec``, ``FixedS
 ffn       ``forward(ops, h, residual, step)``: adds its output to ``residual``.
 block     arrangement of the four parts of a layer: ``forward(ops, x, step, cache)``.
 embedding ``forward(ops, token_ids, out)``;  head ``forward(ops, h) -> logits``.
+junction  ``forward(ops, x, x0, index, step)``: renews the residual stream ``x`` in place from itself
+          and the embedding output ``x0`` where the schedule enters pass ``index`` of a run of layers.
 
 ``h`` is the normed activation in the engine's activation dtype (bfloat16 or
 float32); ``residual``/``x`` is the float32 residual stream ``[T, hidden]``.
@@ -104,7 +106,7 @@ class Part:
 
 
 _REGISTRY: dict[tuple[str, str], Callable[..., Part]] = {}
-CATEGORIES = ("norm", "position", "mixer", "ffn", "block", "embedding", "head")
+CATEGORIES = ("norm", "position", "mixer", "ffn", "block", "embedding", "head", "junction")
 
 
 def register_part(category: str, kind: str, factory: Callable[..., Part]) -> None:

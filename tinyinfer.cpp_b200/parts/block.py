@@ -6,6 +6,9 @@ mixer's and the feed-forward's last product.  A layer without a feed-forward sto
 
 ``parallel``: ``h = norm(x)``, then ``x += mixer(h)`` and ``x += ffn(h)``.
 
+``sandwich``: a norm before and behind each sublayer, ``x += norm1b(mixer(norm1(x)))`` then
+``x += norm2b(ffn(norm2(x)))``.
+
 ``output_norm``: the norm sits on the sublayer's output, ``x += norm1(mixer(x + conv(x)))`` then
 ``x += norm2(ffn(x))``, with an optional short causal convolution over time in front of the mixer
 and an optional weighted sum over the results of all layers so far behind the layer.
@@ -48,6 +51,30 @@ class ParallelBlock(Part):
         self.mixer.forward(ops, h, x, step, cache)
         if self.ffn is not None:
             self.ffn.forward(ops, h, x, step)
+
+
+class SandwichBlock(Part):
+    """``x += post1(mixer(pre1(x)))`` then, where the layer has a feed-forward, ``x += post2(ffn(pre2(x)))``:
+    every sublayer reads a normed input and its output passes a second norm before it joins the
+    float32 residual stream.  The norms behind the sublayers must be able to add to a residual
+    (``add_to``)."""
+    category = "block"
+
+    def __init__(self, mixer, mixer_norm, mixer_post_norm, ffn=None, ffn_norm=None, ffn_post_norm=None):
+        if not ((ffn is None) == (ffn_norm is None) == (ffn_post_norm is None)):
+            raise ValueError("a feed-forward and its two norms come together")
+        self.mixer, self.ffn = mixer, ffn
+        self.mixer_norm, self.mixer_post_norm = mixer_norm, mixer_post_norm
+        self.ffn_norm, self.ffn_post_norm = ffn_norm, ffn_post_norm
+
+    def forward(self, ops, x, step, cache):
+        y = torch.zeros_like(x)
+        self.mixer.forward(ops, self.mixer_norm.forward(ops, x, step.act_dtype), y, step, cache)
+        self.mixer_post_norm.add_to(ops, y, x)
+        if self.ffn is not None:
+            y.zero_()
+            self.ffn.forward(ops, self.ffn_norm.forward(ops, x, step.act_dtype), y, step)
+            self.ffn_post_norm.add_to(ops, y, x)
 
 
 class OutputNormBlock(Part):
@@ -129,4 +156,5 @@ class OutputNormBlock(Part):
 
 register_part("block", "prenorm", PreNormBlock)
 register_part("block", "output_norm", OutputNormBlock)
+register_part("block", "sandwich", SandwichBlock)
 register_part("block", "parallel", ParallelBlock)

@@ -2,7 +2,7 @@
 
 Embedding: ``x[t] = float32(E[token[t]])`` without scaling (reference:
 src/inference.cu:14-24); ``scaled_sinusoid``: the row times a constant plus a sine/cosine
-wave of the token's position; ``normed``: the row under an RMSNorm with a weight of its own.  Head: ``logits = h E_out^T`` in float32, where ``E_out``
+wave of the token's position (``scaled``: the constant alone); ``normed``: the row under an RMSNorm with a weight of its own.  Head: ``logits = h E_out^T`` in float32, where ``E_out``
 is the embedding table when the head is tied (reference: always tied,
 src/inference.cu:70-71) or a table of its own.
 """
@@ -61,6 +61,16 @@ class SinusoidEmbedding(Embedding):
         ops.embed_sinusoid(self.table, token_ids, positions, self.freq, self.scale, out)
 
 
+class ScaledEmbedding(SinusoidEmbedding):
+    """``x[t] = E[token[t]] * scale``: the table's row times a constant, no wave."""
+
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0, tensor: str = "weight"):
+        super().__init__(vocab_size, hidden_size, scale=scale, tensor=tensor)
+
+    def load_weights(self, tensors, ops):
+        self.table = ops.pack_linear(tensors[self.tensor])
+
+
 class NormedEmbedding(Embedding):
     """``x[t] = norm(E[token[t]])``: RMSNorm of the table's row (float32) with a weight of the
     model's width; ``one_plus``: the stored weight is the factor minus one."""
@@ -90,9 +100,12 @@ class NormedEmbedding(Embedding):
 class LMHead(Part):
     category = "head"
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied: bool, tensor: str = "weight"):
+    def __init__(self, vocab_size: int, hidden_size: int, tied: bool, tensor: str = "weight", softcap=None):
         self.vocab_size, self.hidden_size, self.tied = int(vocab_size), int(hidden_size), bool(tied)
         self.tensor = str(tensor)
+        self.softcap = None if softcap is None else float(softcap)
+        if self.softcap is not None and not self.softcap > 0:
+            raise ValueError(f"the logits' cap must be positive, got {softcap}")
         self.table = None
 
     def weight_specs(self):
@@ -110,10 +123,13 @@ class LMHead(Part):
     def forward(self, ops, h):
         logits = torch.empty((h.shape[0], self.vocab_size), dtype=torch.float32, device=h.device)
         ops.linear(h, self.table, logits)
+        if self.softcap is not None:
+            ops.cap_rows(logits, self.softcap)
         return logits
 
 
 register_part("embedding", "embedding", Embedding)
 register_part("embedding", "scaled_sinusoid", SinusoidEmbedding)
+register_part("embedding", "scaled", ScaledEmbedding)
 register_part("embedding", "normed", NormedEmbedding)
 register_part("head", "lm_head", LMHead)

@@ -7,6 +7,10 @@ key is ``Wuk_a c`` and its value ``Wuv_a c``; ``score = (q_plain . k_plain + q_r
 scale``; causal softmax whose denominator also counts ``exp(sink[a])`` (a logit without a value);
 ``residual += Wo (heads)``.
 
+With ``q_rank`` the queries pass a latent of their own: ``c_q = RMSnorm(Wdq h)`` with a weight
+(``dq``, ``dq.norm``), ``q = Wuq c_q`` (``uq``), instead of ``q = Wq h``.  A window limits the keys
+to ``i - j < window``.
+
 Only ``[c | k_rot]`` is cached, one row per token.  The heads' keys and values are never built:
 since ``q_plain . (Wuk_a c) = (Wuk_a^T q_plain) . c``, the query is carried into the latent's space
 (``head_project`` with ``Wuk_a^T``), attention runs with one shared row as key (``rank + dr``
@@ -28,20 +32,25 @@ class LatentAttention(Part):
 
     def __init__(self, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, v_head_dim: int,
                  kv_rank: int, scale: float, norm_eps: float, position: PartSpec, sink: bool = True,
-                 window: Optional[int] = None):
+                 window: Optional[int] = None, q_rank: Optional[int] = None):
         self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
         self.head_dim, self.rot_dim, self.v_head_dim = int(head_dim), int(rot_dim), int(v_head_dim)
         self.rank, self.scale, self.eps = int(kv_rank), float(scale), float(norm_eps)
         self.has_sink = bool(sink)
         self.window = None if window is None else int(window)
+        self.q_rank = None if q_rank is None else int(q_rank)
         self.position = build_part("position", position)
         self.nq = self.num_heads * (self.head_dim + self.rot_dim)
         self.row = self.rank + self.rot_dim
         self.w_in = self.w_o = self.latent_norm = self.sink = self.w_uk = self.w_uv = None
+        self.w_dq = self.w_uq = self.q_norm = None
 
     def weight_specs(self):
         h, nh = self.hidden_size, self.num_heads
-        specs = {"q": WeightSpec((self.nq, h), MATRIX), "dkv": WeightSpec((self.row, h), MATRIX),
+        q = {"q": WeightSpec((self.nq, h), MATRIX)} if self.q_rank is None else {
+            "dq": WeightSpec((self.q_rank, h), MATRIX), "dq.norm": WeightSpec((self.q_rank,), NORM_WEIGHT),
+            "uq": WeightSpec((self.nq, self.q_rank), MATRIX)}
+        specs = {**q, "dkv": WeightSpec((self.row, h), MATRIX),
                  "dkv.norm": WeightSpec((self.rank,), NORM_WEIGHT),
                  "uk": WeightSpec((nh * self.head_dim, self.rank), MATRIX),
                  "uv": WeightSpec((nh * self.v_head_dim, self.rank), MATRIX),
@@ -51,10 +60,15 @@ class LatentAttention(Part):
         return specs
 
     def load_weights(self, tensors, ops):
-        q, dkv = tensors["q"], tensors["dkv"]
-        if q.dtype != dkv.dtype:
-            q, dkv = q.to(torch.float32), dkv.to(torch.float32)
-        self.w_in = ops.pack_linear(torch.cat([q, dkv], dim=0))
+        if self.q_rank is None:
+            q, dkv = tensors["q"], tensors["dkv"]
+            if q.dtype != dkv.dtype:
+                q, dkv = q.to(torch.float32), dkv.to(torch.float32)
+            self.w_in = ops.pack_linear(torch.cat([q, dkv], dim=0))
+        else:
+            self.w_in = ops.pack_linear(tensors["dkv"])
+            self.w_dq, self.w_uq = ops.pack_linear(tensors["dq"]), ops.pack_linear(tensors["uq"])
+            self.q_norm = as_float32(tensors["dq.norm"]).contiguous()
         self.w_o = ops.pack_linear(tensors["o"])
         self.latent_norm = as_float32(tensors["dkv.norm"]).contiguous()
         self.sink = as_float32(tensors["sink"]).contiguous() if self.has_sink else None
@@ -73,10 +87,18 @@ class LatentAttention(Part):
         t, nh = h.shape[0], self.num_heads
         proj = torch.empty((t, self.w_in.shape[0]), dtype=torch.float32, device=h.device)
         ops.linear(h, self.w_in, proj)
+        q_proj = None
+        if self.q_rank is not None:                   # the queries through their own normed latent
+            q_lat = torch.empty((t, self.q_rank), dtype=torch.float32, device=h.device)
+            ops.linear(h, self.w_dq, q_lat)
+            q_lat_n = torch.empty((t, self.q_rank), dtype=h.dtype, device=h.device)
+            ops.rmsnorm(q_lat, self.q_norm, self.eps, q_lat_n)
+            q_proj = torch.empty((t, self.nq), dtype=torch.float32, device=h.device)
+            ops.linear(q_lat_n, self.w_uq, q_proj)
         q_plain = torch.empty((t, nh * self.head_dim), dtype=h.dtype, device=h.device)
         q_full = torch.empty((t, nh, self.row), dtype=h.dtype, device=h.device)
         ops.latent_prepare(proj, self.latent_norm, self.eps, self.position.rotation(h.device), step, cache,
-                           q_plain, q_full, nh, self.head_dim, self.rot_dim, self.rank)
+                           q_plain, q_full, nh, self.head_dim, self.rot_dim, self.rank, q_proj=q_proj)
         ops.head_project(q_plain.view(t, nh, self.head_dim), self.w_uk, q_full[:, :, :self.rank])
         mixed = torch.empty((t, nh, self.rank), dtype=h.dtype, device=h.device)
         ops.attention_options(q_full.view(t, nh * self.row), step, cache, mixed.view(t, nh * self.rank), nh, 1,

@@ -27,6 +27,10 @@ class CausalLM:
             (plan.names["final_norm"], self.final_norm),
             (plan.names["head"], self.head),
         ]
+        self.junction = None
+        if plan.junction is not None:
+            self.junction = build_part("junction", plan.junction)
+            self._named.append((plan.names["junction"], self.junction))
         for lp in plan.layers:
             parts = {
                 "mixer": build_part("mixer", lp.mixer),
@@ -34,6 +38,9 @@ class CausalLM:
                 "mixer_norm": build_part("norm", lp.mixer_norm),
                 "ffn_norm": None if lp.ffn_norm is None else build_part("norm", lp.ffn_norm),
             }
+            for role, spec in (("mixer_post_norm", lp.mixer_post_norm), ("ffn_post_norm", lp.ffn_post_norm)):
+                if spec is not None:             # only blocks that norm a sublayer's output take these
+                    parts[role] = build_part("norm", spec)
             self.blocks.append(build_part("block", lp.block, **parts))
             if "block" in lp.names:            # an arrangement with tensors of its own
                 self._named.append((lp.names["block"], self.blocks[-1]))
@@ -104,7 +111,10 @@ class CausalLM:
             self.embedding.forward(ops, step.token_ids, x, step.positions)
         else:
             self.embedding.forward(ops, step.token_ids, x)
+        x0 = x.clone() if self.junction is not None else None      # the embedding output, for the junction
         for entry in self.plan.schedule:
+            if entry.enter is not None:
+                self.junction.forward(ops, x, x0, entry.enter, step)
             cache = cache_views[(entry.cache_slot, entry.writes_cache)]
             self.blocks[entry.layer].forward(ops, x, step, cache)
         ops.flush()                        # nothing a part asked for may still be held back

@@ -16,6 +16,13 @@ over all experts as weights (not renormalised); ``activation = (kind, limit, alp
 gated activation for the experts (``parts/mlp.py``), and the weight then scales the expert's
 output, ``w Wdown_e act(Wgate_e h, Wup_e h)``; ``shared_gated = False`` leaves the shared expert's
 sigmoid gate out (no ``shared.sg``); ``shared_activation`` is the shared expert's own activation.
+
+With the softmax router three more options.  ``identity = n``: the last ``n`` of the router's
+``experts + n`` outputs are *identity experts* without tensors, whose output is the input ``h``
+itself (times the weight).  ``correction``: a stored vector (``correction``) is added to the scores
+for the choice alone; the weights are the scores without it.  ``groups = (count, keep)``: the router's
+outputs, identity ones included, form ``count`` equal groups of neighbours; a group's value is its
+largest score (with the correction), and only outputs of the ``keep`` best groups can be chosen.
 """
 from __future__ import annotations
 
@@ -23,7 +30,7 @@ from typing import Optional
 
 import torch
 
-from .base import MATRIX, Part, WeightSpec, register_part
+from .base import MATRIX, NORM_ZERO, Part, WeightSpec, as_float32, register_part
 
 
 class RoutedExperts(Part):
@@ -31,9 +38,18 @@ class RoutedExperts(Part):
 
     def __init__(self, hidden_size: int, experts: int, top: int, expert_size: int,
                  shared_size: Optional[int] = None, router: str = "sigmoid", activation=None,
-                 shared_gated: bool = True, shared_activation=None):
-        if not 1 <= top <= experts:
-            raise ValueError(f"{top} of {experts} experts cannot be chosen")
+                 shared_gated: bool = True, shared_activation=None, identity: int = 0, correction: bool = False,
+                 groups=None):
+        self.identity, self.has_correction = int(identity), bool(correction)
+        self.groups = None if groups is None else (int(groups[0]), int(groups[1]))
+        self.routed = int(experts) + self.identity         # the router's outputs
+        if (self.identity or self.has_correction or self.groups) and router != "softmax":
+            raise ValueError("identity experts, a correction and groups come with the softmax router")
+        count, keep = self.groups or (1, 1)
+        if self.identity < 0 or count < 1 or not 1 <= keep <= count or self.routed % count:
+            raise ValueError(f"{self.routed} router outputs do not fall into {count} equal groups of which {keep} are kept")
+        if not 1 <= top <= self.routed // count * keep:
+            raise ValueError(f"{top} of {self.routed // count * keep} experts cannot be chosen")
         self.hidden_size, self.experts, self.top = int(hidden_size), int(experts), int(top)
         self.expert_size = int(expert_size)
         self.shared_size = None if shared_size is None else int(shared_size)
@@ -49,7 +65,9 @@ class RoutedExperts(Part):
 
     def weight_specs(self):
         h, f = self.hidden_size, self.expert_size
-        specs = {"router": WeightSpec((self.experts, h), MATRIX)}
+        specs = {"router": WeightSpec((self.routed, h), MATRIX)}
+        if self.has_correction:
+            specs["correction"] = WeightSpec((self.routed,), NORM_ZERO)
         for e in range(self.experts):
             specs[f"e{e}.gate"] = WeightSpec((f, h), MATRIX)
             specs[f"e{e}.up"] = WeightSpec((f, h), MATRIX)
@@ -85,6 +103,7 @@ class RoutedExperts(Part):
             router.append(torch.zeros((16 - rows % 16, self.hidden_size), dtype=router[0].dtype,
                                       device=router[0].device))
         self.w_router = ops.pack_linear(torch.cat(router, dim=0))
+        self.correction = as_float32(tensors["correction"]).contiguous() if self.has_correction else None
         self.w_experts = ops.pack_experts(stacked("gate"), stacked("up"), stacked("down"))
 
     def forward(self, ops, h, residual, step):
@@ -96,12 +115,20 @@ class RoutedExperts(Part):
         shared_gate = None
         if self.shared_size is not None and self.shared_gated:
             shared_gate = torch.empty((t,), dtype=torch.float32, device=h.device)
-        ops.router_topk(logits, self.experts, self.top, ids, weights, shared_gate, softmax=self.router == "softmax")
+        general = bool(self.identity or self.has_correction or self.groups)
+        if general:
+            count, keep = self.groups or (1, 1)
+            ops.router_choose(logits, self.routed, self.top, ids, weights, self.correction, count, keep)
+        else:
+            ops.router_topk(logits, self.experts, self.top, ids, weights, shared_gate, softmax=self.router == "softmax")
         shared = None
         plain = self.activation is None and self.shared_activation is None and self.shared_gated
         if self.shared_size is not None and plain:
             shared = (self.w_shared_gate_up, self.w_shared_down, shared_gate)
-        ops.routed_experts(h, self.w_experts, ids, weights, residual, shared, act=self.activation)
+        if self.identity:
+            ops.routed_experts(h, self.w_experts, ids, weights, residual, shared, act=self.activation, identity=True)
+        else:
+            ops.routed_experts(h, self.w_experts, ids, weights, residual, shared, act=self.activation)
         if self.shared_size is not None and not plain:
             # a shared expert with an activation of its own, or without a gate: a feed-forward beside the routed ones
             kind, limit, alpha = self.shared_activation or ("silu", 0.0, 0.0)

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import NORM_WEIGHT, Part, WeightSpec, as_float32, register_part
+from .base import NORM_WEIGHT, NORM_ZERO, Part, WeightSpec, as_float32, register_part
 
 
 class RMSNorm(Part):
@@ -82,3 +82,44 @@ class GroupRMSNorm(Part):
 
 
 register_part("norm", "group_rmsnorm", GroupRMSNorm)
+
+
+class DynamicTanh(Part):
+    """A norm that takes no mean and no variance: ``tanh(alpha * x) * w + b`` with one scalar
+    ``alpha``, a weight and a bias per element (tensors ``<tensor>``, ``<tensor>.alpha``,
+    ``<tensor>.b``).  The three forms of ``GroupRMSNorm``: rows out, gathered rows out, and
+    ``add_to`` a float32 residual."""
+    category = "norm"
+
+    def __init__(self, size: int, tensor: str = "weight", bias: bool = True):
+        self.size, self.tensor, self.has_bias = int(size), str(tensor), bool(bias)
+        self.weight = self.bias = None
+        self.alpha = 1.0
+
+    def weight_specs(self):
+        specs = {self.tensor: WeightSpec((self.size,), NORM_WEIGHT), self.tensor + ".alpha": WeightSpec((), NORM_WEIGHT)}
+        if self.has_bias:
+            specs[self.tensor + ".b"] = WeightSpec((self.size,), NORM_ZERO)
+        return specs
+
+    def load_weights(self, tensors, ops):
+        self.weight = as_float32(tensors[self.tensor]).contiguous()
+        self.bias = as_float32(tensors[self.tensor + ".b"]).contiguous() if self.has_bias else None
+        self.alpha = float(as_float32(tensors[self.tensor + ".alpha"]).reshape(()).item())   # a constant of the model
+
+    def forward(self, ops, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        out = torch.empty((x.shape[0], self.size), dtype=out_dtype, device=x.device)
+        ops.tanh_norm(x, self.alpha, self.weight, self.bias, out=out)
+        return out
+
+    def forward_rows(self, ops, x: torch.Tensor, rows: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        out = torch.empty((rows.shape[0], self.size), dtype=out_dtype, device=x.device)
+        ops.tanh_norm(x, self.alpha, self.weight, self.bias, out=out, rows=rows)
+        return out
+
+    def add_to(self, ops, y: torch.Tensor, residual: torch.Tensor) -> None:
+        """``residual += norm(y)``, both float32."""
+        ops.tanh_norm(y, self.alpha, self.weight, self.bias, residual=residual)
+
+
+register_part("norm", "dynamic_tanh", DynamicTanh)

@@ -20,6 +20,9 @@ Kinds built in:
            ``ops.latent_prepare``); the per-head norm kernel of ``neox`` does not.
 ``none``   no rotation (``rotary_dim = 0``).
 
+``rope_stretched`` (YaRN) answers with either pairing: frequencies that turn fast stay, slow ones are
+divided by ``factor``, a ramp lies between; and ``Rotation.scale`` multiplies both sine and cosine.
+
 ``inv_freq`` is computed once on the host in double precision and rounded to float32; the
 angle, its sine and cosine are float32 on the device.
 """
@@ -41,11 +44,14 @@ class Rotation:
     rotary_dim  how many leading elements of a head take part (0: none)
     inv_freq    ``[rotary_dim / 2]`` float32 on the device, or None
     extra       anything else a kind's own handler wants
+    scale       a factor on both the sine and the cosine (1: a pure turn); the kernels that take it
+                say so (``ops.latent_prepare``, ``ops.qkv_turn_store``)
     """
     kind: str
     rotary_dim: int
     inv_freq: Optional[torch.Tensor] = None
     extra: Any = None
+    scale: float = 1.0
 
 
 _TABLES: dict[tuple, torch.Tensor] = {}      # layers with the same constants share one device tensor
@@ -82,6 +88,44 @@ class RopeInterleaved(RopeNeox):
         return Rotation("interleaved", self.rotary_dim, super().rotation(device).inv_freq)
 
 
+class RopeStretched(RopeNeox):
+    """Frequencies stretched for contexts longer than the ``original`` one (YaRN).  With
+    ``d(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta)``, ``lo = max(floor(d(fast)), 0)``,
+    ``hi = min(ceil(d(slow)), rotary_dim - 1)`` and ``ramp_k = clamp((k - lo) / max(hi - lo, 0.001),
+    0, 1)``, pair ``k`` turns with ``f_k / factor * ramp_k + f_k * (1 - ramp_k)``, and sine and
+    cosine are multiplied by ``0.1 ln(factor) + 1``.  ``layout``: ``interleaved`` or ``neox``."""
+
+    def __init__(self, head_dim: int, theta: float, factor: float, original: float, fast: float, slow: float,
+                 rotary_dim: Optional[int] = None, layout: str = "interleaved"):
+        super().__init__(head_dim, theta, rotary_dim)
+        if layout not in ("interleaved", "neox"):
+            raise ValueError(f"pairing {layout!r}; known: interleaved, neox")
+        self.factor, self.original = float(factor), float(original)
+        self.fast, self.slow, self.layout = float(fast), float(slow), layout
+        if not (self.factor > 0 and self.original > 0 and self.fast > 0 and self.slow > 0 and self.theta > 1):
+            raise ValueError("stretched frequencies need positive constants and a base above 1")
+
+    def inv_freq(self) -> torch.Tensor:
+        import math
+        n = self.rotary_dim
+
+        def at(turns: float) -> float:
+            return n * math.log(self.original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+
+        lo, hi = max(math.floor(at(self.fast)), 0), min(math.ceil(at(self.slow)), n - 1)
+        k = torch.arange(n // 2, dtype=torch.float64)
+        plain = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * k / n)
+        ramp = torch.clamp((k - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return (plain / self.factor * ramp + plain * (1.0 - ramp)).to(torch.float32)
+
+    def rotation(self, device) -> Rotation:
+        import math
+        key = ("stretched", self.rotary_dim, self.theta, self.factor, self.original, self.fast, self.slow, str(device))
+        if key not in _TABLES:
+            _TABLES[key] = self.inv_freq().to(device)
+        return Rotation(self.layout, self.rotary_dim, _TABLES[key], scale=0.1 * math.log(self.factor) + 1.0)
+
+
 class NoPosition(Part):
     """Heads are normed and stored without a rotation."""
     category = "position"
@@ -95,4 +139,5 @@ class NoPosition(Part):
 
 register_part("position", "rope_neox", RopeNeox)
 register_part("position", "rope_interleaved", RopeInterleaved)
+register_part("position", "rope_stretched", RopeStretched)
 register_part("position", "none", NoPosition)
