@@ -232,3 +232,11 @@ def forward(cfg, w, tokens, layers_out=None):
     logits = dyt(x, w, "final.norm") @ w["head"].T
     cap = cfg.get("logit_softcap")
     return cap * torch.tanh(logits / cap) if cap else logits
+
+
+def greedy(cfg, w, prompt, n):
+    """``n`` tokens by argmax, each from a whole pass over everything so far."""
+    tokens = list(prompt)
+    for _ in range(n):
+        tokens.append(int(torch.argmax(forward(cfg, w, tokens)[-1])))
+    return tokens[len(prompt):]

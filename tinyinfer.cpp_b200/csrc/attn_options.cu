@@ -98,22 +98,22 @@ qkv_turn_store_kernel(const float* proj, int stride, const float* __restrict__ i
     }
 }
 
-// x[t, h, :] turned by sign * position over its first `rot` elements, then times sigmoid(gate[t, h * n + j])
+// x[t, h, :] turned by sign * position over its first `rot` elements, then times sigmoid(gate[t, h * n + j]);
+// a block per (token, head), so the rows may be turned in place
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 turn_rows_kernel(const T* x, const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot,
                  int halves, float sign, const float* gate, int gate_stride, int num_heads, int n, T* out) {
-    extern __shared__ float head_rows[];               // the token's heads in float32
-    const int t = blockIdx.x, width = num_heads * n;
-    const T* src = x + (size_t)t * width;
-    for (int e = threadIdx.x; e < width; e += blockDim.x) head_rows[e] = to_f32(src[e]);
+    extern __shared__ float head_row[];                // the head in float32
+    const int t = blockIdx.x, h = blockIdx.y;
+    const size_t at = ((size_t)t * num_heads + h) * n;
+    for (int j = threadIdx.x; j < n; j += blockDim.x) head_row[j] = to_f32(x[at + j]);
     __syncthreads();
     const float pos = sign * (float)positions[t];
-    for (int e = threadIdx.x; e < width; e += blockDim.x) {
-        const int j = e % n;
-        float y = turned_at(head_rows + (e - j), j, rot, halves, pos, inv_freq, 1.0f);
-        if (gate) y *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + e]));
-        out[(size_t)t * width + e] = from_f32<T>(y);
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+        float y = turned_at(head_row, j, rot, halves, pos, inv_freq, 1.0f);
+        if (gate) y *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + (size_t)h * n + j]));
+        out[at + j] = from_f32<T>(y);
     }
 }
 
@@ -606,15 +606,16 @@ extern "C" int ti_turn_rows(const void* x, int dtype, const int* positions, cons
     if (num_tokens == 0 || num_heads == 0) return 0;
     TI_REQUIRE(rot >= 0 && rot <= n && rot % 2 == 0, "turn_rows: rotated width %d must be even and at most %d", rot, n);
     TI_REQUIRE(rot == 0 || inv_freq != nullptr, "turn_rows: a rotation needs its frequencies");
-    const size_t smem = (size_t)num_heads * n * sizeof(float);
-    TI_REQUIRE(smem <= 48 * 1024, "turn_rows: rows of %d elements are more than the kernel stages", num_heads * n);
+    const size_t smem = (size_t)n * sizeof(float);
+    TI_REQUIRE(n <= 8192 && num_heads <= 65535, "turn_rows: %d heads of %d elements", num_heads, n);
     cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(num_tokens, num_heads);
     if (dtype == TI_BF16)
-        turn_rows_kernel<bf16><<<num_tokens, 256, smem, s>>>((const bf16*)x, positions, inv_freq, rot, halves, sign, gate,
-                                                            gate_stride, num_heads, n, (bf16*)out);
+        turn_rows_kernel<bf16><<<grid, 128, smem, s>>>((const bf16*)x, positions, inv_freq, rot, halves, sign, gate,
+                                                      gate_stride, num_heads, n, (bf16*)out);
     else if (dtype == TI_F32)
-        turn_rows_kernel<float><<<num_tokens, 256, smem, s>>>((const float*)x, positions, inv_freq, rot, halves, sign,
-                                                             gate, gate_stride, num_heads, n, (float*)out);
+        turn_rows_kernel<float><<<grid, 128, smem, s>>>((const float*)x, positions, inv_freq, rot, halves, sign,
+                                                       gate, gate_stride, num_heads, n, (float*)out);
     else return ti_fail("turn_rows: dtype code %d", dtype);
     return ti_check_launch("turn_rows");
 }
