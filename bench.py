@@ -946,6 +946,154 @@ def reference_arm(args) -> int:
     return 0
 
 
+
+# ---- the Nekorax decoder beside the Ruvuvik decoder at equal sizes ------------------------------
+# (width, heads, kv heads, head size, latent rank, query latent rank, rotated part, window of the latent layers,
+#  taps, experts, identity experts, top, expert ff, groups (count, keep), blocks of [latent attention, attention]
+#  layers; the first block is walked twice)
+NEKORAX_SIZES = {
+    "w1024": (1024, 16, 4, 64, 256, 384, 32, 4096, 4, 12, 4, 4, 704, (4, 2), 2),
+    "w2048": (2048, 16, 4, 128, 512, 768, 64, 4096, 4, 24, 8, 4, 1408, (4, 2), 2),
+    "w4096": (4096, 32, 8, 128, 512, 1536, 64, 4096, 4, 48, 16, 4, 1408, (8, 4), 1),
+}
+
+
+def nekorax_config(size):
+    w, h, g, d, rank, q_rank, dr, window, taps, experts, identity, top, eff, groups, blocks = size
+    mlp = {"kind": "moe", "router": {"experts": experts, "identity": identity, "top": top,
+                                     "groups": {"count": groups[0], "keep": groups[1]}},
+           "expert": {"ff": eff, "limit": 7.0}}
+    layers = [
+        {"type": "latent_attention", "mlp": mlp,
+         "mixer": {"heads": h, "dim": d, "rot_dim": dr, "vdim": d, "kv_rank": rank, "q_rank": q_rank,
+                   "mask": {"size": window}, "scale": (d + dr) ** -0.5,
+                   "rot": {"dims": dr, "base": 10000.0,
+                           "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}},
+        {"type": "attention", "mlp": mlp,
+         "mixer": {"heads": h, "kv_heads": g, "dim": d, "vdim": d, "conv": taps,
+                   "rot": {"dims": d // 2, "base": 250000.0}, "scale": d ** -0.5}}]
+    return {"architecture": "Nekorax", "vocab": DESIGN_VOCAB, "width": w, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "loop": {"start": 0, "stop": 2, "times": 2},
+            "layers": layers * blocks}
+
+
+def ruvuvik_beside_nekorax(size, context):
+    """As many layers as the Nekorax decoder has layer runs, attention and latent attention in turn (no chunk
+    edge inside the context), and a dense feed-forward with as many multiply-adds a token as the chosen experts."""
+    w, h, g, d, rank, q_rank, dr, window, taps, experts, identity, top, eff, groups, blocks = size
+    mlp = {"kind": "dense", "ff": top * eff * 3 // 2 // 64 * 64}
+    layers = [
+        {"type": "latent_attention", "mlp": mlp,
+         "mixer": {"heads": h, "dim": d, "rot_dim": dr, "vdim": d, "kv_rank": rank,
+                   "rot": {"dims": dr, "base": 100000.0}, "scale": (d + dr) ** -0.5}},
+        {"type": "attention", "mlp": mlp,
+         "mixer": {"heads": h, "kv_heads": g, "dim": d, "vdim": d, "mask": {"size": context},
+                   "rot": {"dims": d, "base": 10000.0}, "scale": d ** -0.5, "softcap": 50.0}}]
+    return {"architecture": "Ruvuvik", "vocab": DESIGN_VOCAB, "width": w, "norm": {"eps": 1e-5},
+            "layers": layers * (blocks + 1)}
+
+
+def nekorax_arm(args) -> int:
+    """Prefill and decode throughput of the Nekorax decoder at sizes of real layers, beside the Ruvuvik
+    decoder (the closest design the engine has: the same two attention kernels) with as many layers as
+    Nekorax has layer runs, of the same width, heads, head size and latent rank, and the time the device
+    spends in every kind of kernel call per layer run, with the fraction of the roofline for the calls
+    that have one."""
+    import torch
+    from tinyinfer_b200 import Engine, StepEntry
+    pk, pk_kind = peaks()
+    prompt_len, batch, context = args.prefill_tokens, args.batch, args.context
+    warmup = max(args.warmup, 3)
+    out = {"design": "nekorax", "beside": "ruvuvik at equal sizes", "peaks": pk_kind, "prefill_tokens": prompt_len,
+           "decode_batch": batch, "decode_context": context, "dtype": "bf16", "data": "synthetic", "sizes": {}}
+    gen = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, DESIGN_VOCAB, (prompt_len,), generator=gen).tolist()
+    hbm, tc = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    for key, size in NEKORAX_SIZES.items():
+        if args.design_size and key != args.design_size:
+            continue
+        w, h, kvh, d, rank, q_rank, dr, window, taps, experts, identity, top, eff, groups, blocks = size
+        runs = 2 * (blocks + 1)
+        res = {}
+        calls = {"nekorax": ["attention_options", "qkv_turn_store", "turn_rows", "latent_prepare", "head_project",
+                             "causal_conv", "conv_tail_store", "tanh_norm", "tanh_norm_pair", "router_choose", "routed_experts", "add_row",
+                             "cap_rows", "rmsnorm", "linear"],
+                 "ruvuvik": ["attention_options", "qk_rownorm_rope_store", "latent_prepare", "head_project",
+                             "linear_xielu", "xielu_rows", "linear", "rmsnorm"]}
+        for arm, cfg in (("nekorax", nekorax_config(size)),
+                         ("ruvuvik", ruvuvik_beside_nekorax(size, max(context, prompt_len) + 64))):
+            engine = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=args.page_size,
+                            num_pages=-(-max(batch * context, prompt_len) // args.page_size) + batch + 2,
+                            max_requests=batch + 1, step_graphs=True)
+            pf_ms = measure_prefill(engine, prompt_len, max(1, min(args.steps, 6)), torch)
+            ms, clocks, launches = measure_decode(engine, batch, context, args.steps, warmup, torch)
+            a = {"prefill_tok_s": round(prompt_len / pf_ms * 1e3), "prefill_ms": round(pf_ms, 3),
+                 "decode_tok_s": round(batch / ms * 1e3, 1), "decode_ms_per_step": round(ms, 4),
+                 "decode_launches_per_step": launches // max(1, args.steps), "clocks": clocks}
+            engine._step_graphs = None
+            engine.ops.fuse_decode_tail = engine.ops.fuse_decode_ffn = False   # every call of its own
+            names = calls[arm]
+            for _ in range(2):        # the first eager step sizes the allocator's pool; the second is read
+                spans = timed_ops(engine, names, lambda: engine.step([StepEntry("p", prompt, [prompt_len - 1])]), torch)
+                engine.finish("p")
+            ids = fill_requests(engine, batch, context - 4, torch)
+            for _ in range(2):
+                dspans = timed_ops(engine, names, lambda: engine.step([StepEntry(r, [1], [0]) for r in ids]), torch)
+            for r in ids:
+                engine.finish(r)
+            a["calls_us"] = {
+                "prompt": {n: [round(x * 1e3, 1) for x in v[:12]] for n, v in spans.items() if not n.startswith("_") and n != "linear"},
+                "decode": {n: [round(x * 1e3, 1) for x in v[:12]] for n, v in dspans.items() if not n.startswith("_") and n != "linear"}}
+            a["per_layer_us"] = {
+                "prompt": {n: round(sum(v) / runs * 1e3, 1) for n, v in spans.items() if not n.startswith("_")},
+                "decode": {n: round(sum(v) / runs * 1e3, 1) for n, v in dspans.items() if not n.startswith("_")}}
+            seen_all = prompt_len * (prompt_len + 1) / 2
+            row = rank + dr
+
+            def frac(amount, ms_, peak):
+                return round(amount / (ms_ * 1e-3) / peak, 4)
+
+            # calls in layer order: the latent layer first, then the attention layer
+            att, datt = spans["attention_options"], dspans["attention_options"]
+            if arm == "nekorax":
+                seen_window = sum(min(i + 1, window) for i in range(prompt_len))
+                real = top * experts / (experts + identity)            # chosen experts a token that have tensors, if all are alike
+                cols = (h + 2 * kvh) * d
+                a["roofline_frac"] = {
+                    "prompt_latent_attention": frac(2.0 * h * (row + rank) * seen_window, att[0], tc),
+                    "prompt_attention": frac(4.0 * h * d * seen_all, att[1], tc),
+                    "decode_latent_attention": frac(batch * min(context, window) * row * 2.0, datt[0], hbm),
+                    "decode_attention": frac(batch * kvh * context * 2 * d * 2.0, datt[1], hbm),
+                    "prompt_experts": frac(2.0 * prompt_len * real * 3 * w * eff, spans["routed_experts"][0], tc),
+                    "decode_experts": frac(2.0 * 3 * w * eff * min(experts, batch * real), dspans["routed_experts"][0], hbm),
+                    # the row kernels, by the bytes they must move: float32 rows in, rows of the activation dtype or
+                    # float32 rows out
+                    "prompt_norm_by_tanh": frac(prompt_len * w * (4 + 2.0), spans["tanh_norm"][0], hbm),
+                    "prompt_norm_pair": frac(prompt_len * w * (4 + 4 + 4 + 2.0), spans["tanh_norm_pair"][0], hbm),
+                    "prompt_convolution": frac(prompt_len * cols * 8.0, spans["causal_conv"][2], hbm),      # behind the junction's two conversions
+                    "prompt_turn_and_store": frac(prompt_len * cols * (4 + 2.0), spans["qkv_turn_store"][0], hbm),
+                    "prompt_turn_back_and_gate": frac(prompt_len * h * d * (2 + 4 + 2.0), spans["turn_rows"][0], hbm)}
+            else:
+                ffn = {n: sp["linear_xielu"][0] for n, sp in (("prompt", spans), ("decode", dspans))}
+                a["roofline_frac"] = {
+                    "prompt_latent_attention": frac(2.0 * h * (row + rank) * seen_all, att[0], tc),
+                    "prompt_attention": frac(4.0 * h * d * seen_all, att[1], tc),
+                    "decode_latent_attention": frac(batch * context * row * 2.0, datt[0], hbm),
+                    "decode_attention": frac(batch * kvh * context * 2 * d * 2.0, datt[1], hbm),
+                    "prompt_ffn_first_product": frac(2.0 * prompt_len * w * (top * eff * 3 // 2 // 64 * 64), ffn["prompt"], tc),
+                    "decode_ffn_first_product": frac(2.0 * w * (top * eff * 3 // 2 // 64 * 64), ffn["decode"], hbm),
+                    "prompt_norm": frac(prompt_len * w * (4 + 2.0), spans["rmsnorm"][0], hbm),
+                    "prompt_norm_turn_and_store": frac(prompt_len * (h + 2 * kvh) * d * (4 + 2.0), spans["qk_rownorm_rope_store"][0], hbm)}
+            res[arm] = a
+            del engine
+            torch.cuda.empty_cache()
+        out["sizes"][key] = {"width": w, "heads": h, "kv_heads": kvh, "head_dim": d, "kv_rank": rank, "q_rank": q_rank,
+                             "rot_dim": dr, "window": window, "taps": taps, "experts": experts, "identity": identity,
+                             "top": top, "expert_ff": eff, "groups": list(groups), "layer_runs": runs, **res}
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -965,9 +1113,9 @@ def main() -> int:
                     help="with --only mixed: the number of decoding requests beside the 512-token portion")
     ap.add_argument("--attention-in-turn", action="store_true",
                     help="with --only mixed: flash-decoding behind the prompt attention kernel, not beside it")
-    ap.add_argument("--design", choices=["kagorax", "ruvuvik", "feruzen"], default=None,
-                    help="set this decoder beside the closest one the engine has (Qwen3; for feruzen: Ruvuvik) at equal sizes instead of the default run")
-    ap.add_argument("--design-size", choices=sorted(set(DESIGN_SIZES) | set(RUVUVIK_SIZES) | set(FERUZEN_SIZES)), default=None,
+    ap.add_argument("--design", choices=["kagorax", "ruvuvik", "feruzen", "nekorax"], default=None,
+                    help="set this decoder beside the closest one the engine has (Qwen3; for feruzen and nekorax: Ruvuvik) at equal sizes instead of the default run")
+    ap.add_argument("--design-size", choices=sorted(set(DESIGN_SIZES) | set(RUVUVIK_SIZES) | set(FERUZEN_SIZES) | set(NEKORAX_SIZES)), default=None,
                     help="one of the sizes only")
     ap.add_argument("--only", choices=["decode", "prefill", "chains", "mixed"], default=None,
                     help="run one part only and print a short line (for profiling small cases)")
@@ -983,6 +1131,8 @@ def main() -> int:
         return ruvuvik_arm(args)
     if args.design == "feruzen":
         return feruzen_arm(args)
+    if args.design == "nekorax":
+        return nekorax_arm(args)
     if args.design:
         return design_arm(args)
 

@@ -81,6 +81,14 @@ def test_norm_by_tanh(ops, sizes, dtype):
     _close(residual - before, want, torch.float32, "added to a residual")
     ops.tanh_norm(xd, 0.37, wd, None, out=out)
     _close(out, want - w["n.b"].double(), dtype, "without a bias")
+    # the norm behind a sublayer and the norm in front of the next in one launch: the same bits
+    w2, b2 = (1 + 0.3 * torch.randn((n,), generator=g)).to(DEV), (0.2 * torch.randn((n,), generator=g)).to(DEV)
+    first, second = before.clone(), before.clone()
+    ops.tanh_norm(xd, 0.37, wd, bd, residual=first)
+    ops.tanh_norm(first, 1.4, w2, b2, out=out)
+    both = torch.empty_like(out)
+    ops.tanh_norm_pair(xd, 0.37, wd, bd, second, 1.4, w2, b2, both)
+    assert torch.equal(first, second) and torch.equal(out, both)
 
 
 def test_cap_and_added_row(ops):

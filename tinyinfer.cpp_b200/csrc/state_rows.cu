@@ -15,6 +15,8 @@
 //  * add_scaled: dst += sa a + sb b.
 //  * tanh_norm_rows: the norm without a mean or a variance, y = tanh(alpha x) w + b with one scalar alpha;
 //    stored (optionally for gathered rows) or added to a float32 residual, like the norm in groups.
+//    tanh_norm_pair: such a norm's rows are added to the residual and the sum passes a second such norm in the
+//    same launch (the norm behind one sublayer and the norm in front of the next).
 //  * cap_rows: x = cap tanh(x / cap), in place.
 //  * add_row: x[t] += row for every row of x.
 //  * glu_rows: y = act(gate, up) over a float32 product that holds gate and up columns (stacked, or
@@ -171,6 +173,22 @@ __global__ void tanh_norm_rows_kernel(const float* __restrict__ x, const int* __
     else out[i] = from_f32<TO>(y);
 }
 
+// residual += tanh(a1 y) w1 + b1, then out = tanh(a2 residual) w2 + b2
+template <typename TO>
+__global__ void tanh_norm_pair_kernel(const float* __restrict__ y, int n, size_t total, float a1,
+                                      const float* __restrict__ w1, const float* __restrict__ b1, float* residual,
+                                      int res_stride, float a2, const float* __restrict__ w2,
+                                      const float* __restrict__ b2, TO* __restrict__ out) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t r = i / n;
+    const int c = (int)(i % n);
+    float* x = residual + r * res_stride + c;
+    const float sum = *x + fmaf(tanhf(a1 * y[i]), w1[c], b1 ? b1[c] : 0.0f);
+    *x = sum;
+    out[i] = from_f32<TO>(fmaf(tanhf(a2 * sum), w2[c], b2 ? b2[c] : 0.0f));
+}
+
 __global__ void cap_rows_kernel(float* __restrict__ x, size_t total, float cap) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < total) x[i] = cap * tanhf(x[i] / cap);
@@ -300,4 +318,19 @@ extern "C" int ti_add_row(float* x, int stride, const float* row, int rows, int 
     if (total == 0) return 0;
     add_row_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, stride, row, cols, total);
     return ti_check_launch("add_row");
+}
+
+extern "C" int ti_tanh_norm_pair(const float* y, int num_rows, int n, float a1, const float* w1, const float* b1,
+                                 float* residual, int res_stride, float a2, const float* w2, const float* b2, void* out,
+                                 int out_dtype, void* stream) {
+    const size_t total = (size_t)num_rows * n;
+    if (total == 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == TI_BF16)
+        tanh_norm_pair_kernel<bf16><<<blocks, 256, 0, s>>>(y, n, total, a1, w1, b1, residual, res_stride, a2, w2, b2, (bf16*)out);
+    else if (out_dtype == TI_F32)
+        tanh_norm_pair_kernel<float><<<blocks, 256, 0, s>>>(y, n, total, a1, w1, b1, residual, res_stride, a2, w2, b2, (float*)out);
+    else return ti_fail("tanh_norm_pair: output dtype code %d", out_dtype);
+    return ti_check_launch("tanh_norm_pair");
 }

@@ -10,6 +10,7 @@ causal_conv(x, w, step, state, offset, out, add_input, silu)   y = [x +] conv(x)
 conv_tail_store(x, taps, step, state, offset)                  the state's kept inputs renewed after a step
 group_norm(x, w, eps, groups, out | residual, rows)            RMS norm in equal consecutive parts of a row
 tanh_norm(x, alpha, w, b, out | residual, rows)                tanh(alpha x) w + b, the norm without mean or variance
+tanh_norm_pair(y, ..., residual, ..., out)                     residual += norm1(y); out = norm2(residual)
 cap_rows(x, cap)                                               x = cap tanh(x / cap), in place
 add_row(x, row)                                                x[t] += row
 depth_mix(x, hist, index, weights)                             hist[index] = x; x = sum_j weights[j] hist[j]
@@ -69,6 +70,7 @@ class StateOps:
             b.ti_conv_tail_store.argtypes = [_vp, _i, _i, _i, _vp, _vp, _i, _vp, _ll, _ll, _vp]
             b.ti_group_norm_rows.argtypes = [_vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _vp, _i, _vp]
             b.ti_tanh_norm_rows.argtypes = [_vp, _vp, _i, _i, _f, _vp, _vp, _vp, _i, _vp, _i, _vp]
+            b.ti_tanh_norm_pair.argtypes = [_vp, _i, _i, _f, _vp, _vp, _vp, _i, _f, _vp, _vp, _vp, _i, _vp]
             b.ti_cap_rows.argtypes = [_vp, _ll, _f, _vp]
             b.ti_add_row.argtypes = [_vp, _i, _vp, _i, _i, _vp]
             b.ti_depth_mix.argtypes = [_vp, _vp, _ll, _i, _vp, _vp]
@@ -169,6 +171,22 @@ class StateOps:
             x.data_ptr(), _ptr(rows), num, n, float(alpha), weight.data_ptr(), _ptr(bias), _ptr(out),
             _CODE[out.dtype] if out is not None else 0, _ptr(residual),
             residual.stride(0) if residual is not None else 0, self._stream()))
+
+    def tanh_norm_pair(self, y, alpha1, weight1, bias1, residual, alpha2, weight2, bias2, out):
+        """``residual += tanh(alpha1 y) weight1 + bias1``, then ``out = tanh(alpha2 residual) weight2 +
+        bias2``: the norm behind one sublayer and the norm in front of the next, in one launch.  The
+        float32 sum is the same as by ``tanh_norm`` twice."""
+        n = y.shape[1]
+        self._want(y.dtype == torch.float32 and y.is_contiguous() and residual.dtype == torch.float32
+                   and residual.stride(1) == 1 and tuple(residual.shape) == tuple(y.shape) and out.is_contiguous()
+                   and tuple(out.shape) == tuple(y.shape), "tanh_norm_pair: float32 rows, a residual and an output of their shape")
+        for v in (weight1, bias1, weight2, bias2):
+            self._want(v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.shape[0] == n),
+                       "tanh_norm_pair: float32 weights and biases per element")
+        self._rw(self.rows_lib.ti_tanh_norm_pair(
+            y.data_ptr(), y.shape[0], n, float(alpha1), weight1.data_ptr(), _ptr(bias1), residual.data_ptr(),
+            residual.stride(0), float(alpha2), weight2.data_ptr(), _ptr(bias2), out.data_ptr(), _CODE[out.dtype],
+            self._stream()))
 
     def cap_rows(self, x, cap):
         """``x = cap tanh(x / cap)`` over a contiguous float32 tensor, in place."""

@@ -70,11 +70,17 @@ class SandwichBlock(Part):
     def forward(self, ops, x, step, cache):
         y = torch.zeros_like(x)
         self.mixer.forward(ops, self.mixer_norm.forward(ops, x, step.act_dtype), y, step, cache)
-        self.mixer_post_norm.add_to(ops, y, x)
-        if self.ffn is not None:
-            y.zero_()
-            self.ffn.forward(ops, self.ffn_norm.forward(ops, x, step.act_dtype), y, step)
-            self.ffn_post_norm.add_to(ops, y, x)
+        if self.ffn is None:
+            self.mixer_post_norm.add_to(ops, y, x)
+            return
+        if hasattr(self.mixer_post_norm, "add_then") and type(self.ffn_norm) is type(self.mixer_post_norm):
+            h = self.mixer_post_norm.add_then(ops, y, x, self.ffn_norm, step.act_dtype)     # both norms in one launch
+        else:
+            self.mixer_post_norm.add_to(ops, y, x)
+            h = self.ffn_norm.forward(ops, x, step.act_dtype)
+        y.zero_()
+        self.ffn.forward(ops, h, y, step)
+        self.ffn_post_norm.add_to(ops, y, x)
 
 
 class OutputNormBlock(Part):

@@ -121,5 +121,12 @@ class DynamicTanh(Part):
         """``residual += norm(y)``, both float32."""
         ops.tanh_norm(y, self.alpha, self.weight, self.bias, residual=residual)
 
+    def add_then(self, ops, y: torch.Tensor, residual: torch.Tensor, then: "DynamicTanh",
+                 out_dtype: torch.dtype) -> torch.Tensor:
+        """``residual += norm(y)`` and ``then``'s norm of the sum, in one launch."""
+        out = torch.empty((y.shape[0], self.size), dtype=out_dtype, device=y.device)
+        ops.tanh_norm_pair(y, self.alpha, self.weight, self.bias, residual, then.alpha, then.weight, then.bias, out)
+        return out
+
 
 register_part("norm", "dynamic_tanh", DynamicTanh)
