@@ -1025,6 +1025,13 @@ def nekorax_arm(args) -> int:
             engine = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=args.page_size,
                             num_pages=-(-max(batch * context, prompt_len) // args.page_size) + batch + 2,
                             max_requests=batch + 1, step_graphs=True)
+            if arm == "nekorax":
+                # seeded weights are small: every token's scores would be nearly equal and the seeded correction alone
+                # would send all tokens to the same experts.  Larger router rows and no correction make the choice
+                # differ from token to token.
+                for block in engine.model.blocks:
+                    block.ffn.w_router.mul_(6.0)
+                    block.ffn.correction.zero_()
             pf_ms = measure_prefill(engine, prompt_len, max(1, min(args.steps, 6)), torch)
             ms, clocks, launches = measure_decode(engine, batch, context, args.steps, warmup, torch)
             a = {"prefill_tok_s": round(prompt_len / pf_ms * 1e3), "prefill_ms": round(pf_ms, 3),
@@ -1038,9 +1045,28 @@ def nekorax_arm(args) -> int:
                 engine.finish("p")
             ids = fill_requests(engine, batch, context - 4, torch)
             for _ in range(2):
-                dspans = timed_ops(engine, names, lambda: engine.step([StepEntry(r, [1], [0]) for r in ids]), torch)
+                # a token of its own for every request, so that the routers' choices differ between them
+                dspans = timed_ops(engine, names, lambda: engine.step([StepEntry(r, [1 + 37 * i], [0]) for i, r in enumerate(ids)]), torch)
+            chosen = {"prompt": [], "decode": []}
+            if arm == "nekorax":
+                # which experts the first feed-forward's router chose, in a prompt and in a decoding step: the
+                # pairs that have tensors (the rest are identity experts) and how many different experts they hit
+                inner = engine.ops.routed_experts
+
+                def noting(h_, w_, ids_, *rest, **kw):
+                    chosen[phase].append(ids_.clone())
+                    return inner(h_, w_, ids_, *rest, **kw)
+
+                engine.ops.routed_experts = noting
+                phase = "decode"
+                engine.step([StepEntry(r, [1 + 37 * i], [0]) for i, r in enumerate(ids)])
             for r in ids:
                 engine.finish(r)
+            if arm == "nekorax":
+                phase = "prompt"
+                engine.step([StepEntry("p", prompt, [prompt_len - 1])])
+                engine.finish("p")
+                del engine.ops.routed_experts
             a["calls_us"] = {
                 "prompt": {n: [round(x * 1e3, 1) for x in v[:12]] for n, v in spans.items() if not n.startswith("_") and n != "linear"},
                 "decode": {n: [round(x * 1e3, 1) for x in v[:12]] for n, v in dspans.items() if not n.startswith("_") and n != "linear"}}
@@ -1057,15 +1083,18 @@ def nekorax_arm(args) -> int:
             att, datt = spans["attention_options"], dspans["attention_options"]
             if arm == "nekorax":
                 seen_window = sum(min(i + 1, window) for i in range(prompt_len))
-                real = top * experts / (experts + identity)            # chosen experts a token that have tensors, if all are alike
+                first = {k: v[0][v[0] < experts] for k, v in chosen.items()}
+                real_pairs, hit = int(first["prompt"].numel()), int(first["decode"].unique().numel())
+                a["first_router"] = {"prompt_pairs_with_tensors": real_pairs, "of": prompt_len * top,
+                                     "decode_experts_hit": hit, "decode_pairs_with_tensors": int(first["decode"].numel())}
                 cols = (h + 2 * kvh) * d
                 a["roofline_frac"] = {
                     "prompt_latent_attention": frac(2.0 * h * (row + rank) * seen_window, att[0], tc),
                     "prompt_attention": frac(4.0 * h * d * seen_all, att[1], tc),
                     "decode_latent_attention": frac(batch * min(context, window) * row * 2.0, datt[0], hbm),
                     "decode_attention": frac(batch * kvh * context * 2 * d * 2.0, datt[1], hbm),
-                    "prompt_experts": frac(2.0 * prompt_len * real * 3 * w * eff, spans["routed_experts"][0], tc),
-                    "decode_experts": frac(2.0 * 3 * w * eff * min(experts, batch * real), dspans["routed_experts"][0], hbm),
+                    "prompt_experts": frac(2.0 * real_pairs * 3 * w * eff, spans["routed_experts"][0], tc),
+                    "decode_experts": frac(2.0 * 3 * w * eff * hit, dspans["routed_experts"][0], hbm),
                     # the row kernels, by the bytes they must move: float32 rows in, rows of the activation dtype or
                     # float32 rows out
                     "prompt_norm_by_tanh": frac(prompt_len * w * (4 + 2.0), spans["tanh_norm"][0], hbm),

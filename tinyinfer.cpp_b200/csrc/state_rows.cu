@@ -24,6 +24,8 @@
 //    y = g sigmoid(alpha g) (u + 1).
 //
 // All arithmetic is float32.
+#include <initializer_list>
+
 #include "common.cuh"
 #include "glu.cuh"
 
@@ -158,35 +160,79 @@ glu_rows_kernel(const float* gu, int inter, size_t total, int interleaved, int k
     out[i] = from_f32<TO>(glu_activation(kind, row[gate_at], row[up_at], limit, alpha));
 }
 
-// y = tanh(alpha x) w + b over rows of n elements: element-wise, so a thread per element
-template <typename TO, bool ADD>
-__global__ void tanh_norm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, int n, size_t total,
-                                      float alpha, const float* __restrict__ w, const float* __restrict__ b,
-                                      TO* __restrict__ out, float* residual, int res_stride) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= total) return;
-    const size_t r = i / n;
-    const int c = (int)(i % n);
-    const size_t src = rows ? (size_t)rows[r] : r;
-    const float y = fmaf(tanhf(alpha * x[src * n + c]), w[c], b ? b[c] : 0.0f);
-    if constexpr (ADD) residual[r * res_stride + c] += y;
-    else out[i] = from_f32<TO>(y);
+// y = tanh(alpha x) w + b over rows of n elements: element-wise; a block row of the grid per row of x, a thread
+// four neighbouring columns (one 16-byte load) where the rows allow, else one
+template <typename TO> __device__ __forceinline__ void store4(TO* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 raw;
+    raw.x = *reinterpret_cast<unsigned*>(&lo);
+    raw.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+__device__ __forceinline__ float tanh_norm_one(float x, float alpha, float w, float b) { return fmaf(tanhf(alpha * x), w, b); }
+
+template <typename TO, bool ADD, int VEC>
+__global__ void __launch_bounds__(256)
+tanh_norm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, int n, float alpha,
+                      const float* __restrict__ w, const float* __restrict__ b, TO* __restrict__ out,
+                      float* residual, int res_stride) {
+    const size_t r = blockIdx.x;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+    if (c >= n) return;
+    const float* src = x + (rows ? (size_t)rows[r] : r) * n + c;
+    if constexpr (VEC == 4) {
+        const float4 v = *reinterpret_cast<const float4*>(src), wv = *reinterpret_cast<const float4*>(w + c);
+        const float4 bv = b ? *reinterpret_cast<const float4*>(b + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const float y0 = tanh_norm_one(v.x, alpha, wv.x, bv.x), y1 = tanh_norm_one(v.y, alpha, wv.y, bv.y);
+        const float y2 = tanh_norm_one(v.z, alpha, wv.z, bv.z), y3 = tanh_norm_one(v.w, alpha, wv.w, bv.w);
+        if constexpr (ADD) {
+            float4* dst = reinterpret_cast<float4*>(residual + r * res_stride + c);
+            float4 o = *dst;
+            o.x += y0; o.y += y1; o.z += y2; o.w += y3;
+            *dst = o;
+        } else {
+            store4<TO>(out + r * n + c, y0, y1, y2, y3);
+        }
+    } else {
+        const float y = tanh_norm_one(*src, alpha, w[c], b ? b[c] : 0.0f);
+        if constexpr (ADD) residual[r * res_stride + c] += y;
+        else out[r * n + c] = from_f32<TO>(y);
+    }
 }
 
 // residual += tanh(a1 y) w1 + b1, then out = tanh(a2 residual) w2 + b2
-template <typename TO>
-__global__ void tanh_norm_pair_kernel(const float* __restrict__ y, int n, size_t total, float a1,
-                                      const float* __restrict__ w1, const float* __restrict__ b1, float* residual,
-                                      int res_stride, float a2, const float* __restrict__ w2,
-                                      const float* __restrict__ b2, TO* __restrict__ out) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= total) return;
-    const size_t r = i / n;
-    const int c = (int)(i % n);
-    float* x = residual + r * res_stride + c;
-    const float sum = *x + fmaf(tanhf(a1 * y[i]), w1[c], b1 ? b1[c] : 0.0f);
-    *x = sum;
-    out[i] = from_f32<TO>(fmaf(tanhf(a2 * sum), w2[c], b2 ? b2[c] : 0.0f));
+template <typename TO, int VEC>
+__global__ void __launch_bounds__(256)
+tanh_norm_pair_kernel(const float* __restrict__ y, int n, float a1, const float* __restrict__ w1,
+                      const float* __restrict__ b1, float* residual, int res_stride, float a2,
+                      const float* __restrict__ w2, const float* __restrict__ b2, TO* __restrict__ out) {
+    const size_t r = blockIdx.x;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+    if (c >= n) return;
+    if constexpr (VEC == 4) {
+        const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const float4 v = *reinterpret_cast<const float4*>(y + r * n + c);
+        const float4 w1v = *reinterpret_cast<const float4*>(w1 + c), w2v = *reinterpret_cast<const float4*>(w2 + c);
+        const float4 b1v = b1 ? *reinterpret_cast<const float4*>(b1 + c) : zero;
+        const float4 b2v = b2 ? *reinterpret_cast<const float4*>(b2 + c) : zero;
+        float4* dst = reinterpret_cast<float4*>(residual + r * res_stride + c);
+        float4 o = *dst;
+        o.x += tanh_norm_one(v.x, a1, w1v.x, b1v.x); o.y += tanh_norm_one(v.y, a1, w1v.y, b1v.y);
+        o.z += tanh_norm_one(v.z, a1, w1v.z, b1v.z); o.w += tanh_norm_one(v.w, a1, w1v.w, b1v.w);
+        *dst = o;
+        store4<TO>(out + r * n + c, tanh_norm_one(o.x, a2, w2v.x, b2v.x), tanh_norm_one(o.y, a2, w2v.y, b2v.y),
+                   tanh_norm_one(o.z, a2, w2v.z, b2v.z), tanh_norm_one(o.w, a2, w2v.w, b2v.w));
+    } else {
+        float* x = residual + r * res_stride + c;
+        const float sum = *x + tanh_norm_one(y[r * n + c], a1, w1[c], b1 ? b1[c] : 0.0f);
+        *x = sum;
+        out[r * n + c] = from_f32<TO>(tanh_norm_one(sum, a2, w2[c], b2 ? b2[c] : 0.0f));
+    }
 }
 
 __global__ void cap_rows_kernel(float* __restrict__ x, size_t total, float cap) {
@@ -287,22 +333,34 @@ extern "C" int ti_glu_rows(const float* gu, int num_tokens, int inter, int inter
     return ti_check_launch("glu_rows");
 }
 
+static bool rows_of_four(int n, int res_stride, std::initializer_list<const void*> ptrs) {
+    if (n % 4 || res_stride % 4) return false;
+    for (const void* p : ptrs)
+        if ((uintptr_t)p % 16) return false;
+    return true;
+}
+
 extern "C" int ti_tanh_norm_rows(const float* x, const int* rows, int num_rows, int n, float alpha, const float* w,
                                  const float* b, void* out, int out_dtype, float* residual, int res_stride, void* stream) {
-    const size_t total = (size_t)num_rows * n;
-    if (total == 0) return 0;
-    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (num_rows == 0 || n == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
+    const bool four = rows_of_four(n, residual ? res_stride : 0, {x, w, b, out, residual});
+    const dim3 grid(num_rows, (n + (four ? 1023 : 255)) / (four ? 1024 : 256));
+    TI_REQUIRE(grid.y <= 65535, "tanh_norm_rows: rows of %d elements", n);
+#define CALL(TO, ADD, VEC)                                                                            \
+    tanh_norm_rows_kernel<TO, ADD, VEC><<<grid, 256, 0, s>>>(x, rows, n, alpha, w, b, (TO*)(ADD ? nullptr : out), \
+                                                             residual, res_stride)
     if (residual != nullptr) {
         TI_REQUIRE(rows == nullptr, "tanh_norm_rows: rows are not gathered when adding to a residual");
-        tanh_norm_rows_kernel<float, true><<<blocks, 256, 0, s>>>(x, rows, n, total, alpha, w, b, nullptr, residual, res_stride);
+        if (four) CALL(float, true, 4); else CALL(float, true, 1);
     } else if (out_dtype == TI_BF16) {
-        tanh_norm_rows_kernel<bf16, false><<<blocks, 256, 0, s>>>(x, rows, n, total, alpha, w, b, (bf16*)out, nullptr, 0);
+        if (four) CALL(bf16, false, 4); else CALL(bf16, false, 1);
     } else if (out_dtype == TI_F32) {
-        tanh_norm_rows_kernel<float, false><<<blocks, 256, 0, s>>>(x, rows, n, total, alpha, w, b, (float*)out, nullptr, 0);
+        if (four) CALL(float, false, 4); else CALL(float, false, 1);
     } else {
         return ti_fail("tanh_norm_rows: output dtype code %d", out_dtype);
     }
+#undef CALL
     return ti_check_launch("tanh_norm_rows");
 }
 
@@ -323,14 +381,16 @@ extern "C" int ti_add_row(float* x, int stride, const float* row, int rows, int 
 extern "C" int ti_tanh_norm_pair(const float* y, int num_rows, int n, float a1, const float* w1, const float* b1,
                                  float* residual, int res_stride, float a2, const float* w2, const float* b2, void* out,
                                  int out_dtype, void* stream) {
-    const size_t total = (size_t)num_rows * n;
-    if (total == 0) return 0;
-    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (num_rows == 0 || n == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    if (out_dtype == TI_BF16)
-        tanh_norm_pair_kernel<bf16><<<blocks, 256, 0, s>>>(y, n, total, a1, w1, b1, residual, res_stride, a2, w2, b2, (bf16*)out);
-    else if (out_dtype == TI_F32)
-        tanh_norm_pair_kernel<float><<<blocks, 256, 0, s>>>(y, n, total, a1, w1, b1, residual, res_stride, a2, w2, b2, (float*)out);
+    const bool four = rows_of_four(n, res_stride, {y, w1, b1, w2, b2, out, residual});
+    const dim3 grid(num_rows, (n + (four ? 1023 : 255)) / (four ? 1024 : 256));
+    TI_REQUIRE(grid.y <= 65535, "tanh_norm_pair: rows of %d elements", n);
+#define CALL(TO, VEC) \
+    tanh_norm_pair_kernel<TO, VEC><<<grid, 256, 0, s>>>(y, n, a1, w1, b1, residual, res_stride, a2, w2, b2, (TO*)out)
+    if (out_dtype == TI_BF16) { if (four) CALL(bf16, 4); else CALL(bf16, 1); }
+    else if (out_dtype == TI_F32) { if (four) CALL(float, 4); else CALL(float, 1); }
     else return ti_fail("tanh_norm_pair: output dtype code %d", out_dtype);
+#undef CALL
     return ti_check_launch("tanh_norm_pair");
 }
