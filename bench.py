@@ -1017,7 +1017,7 @@ def nekorax_arm(args) -> int:
         res = {}
         calls = {"nekorax": ["attention_options", "qkv_turn_store", "turn_rows", "latent_prepare", "head_project",
                              "causal_conv", "conv_tail_store", "tanh_norm", "tanh_norm_pair", "router_choose", "routed_experts", "add_row",
-                             "cap_rows", "rmsnorm", "linear"],
+                             "cap_rows", "slice_rmsnorm", "linear"],
                  "ruvuvik": ["attention_options", "qk_rownorm_rope_store", "latent_prepare", "head_project",
                              "linear_xielu", "xielu_rows", "linear", "rmsnorm"]}
         for arm, cfg in (("nekorax", nekorax_config(size)),

@@ -91,6 +91,19 @@ def test_norm_by_tanh(ops, sizes, dtype):
     assert torch.equal(first, second) and torch.equal(out, both)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_of_a_column_slice(ops, dtype):
+    g = torch.Generator().manual_seed(4)
+    wide = torch.randn((37, 150), generator=g) * 2
+    w = 1 + 0.3 * torch.randn((40,), generator=g)
+    for lo, weight in ((0, w), (64, w), (110, None)):
+        x = wide[:, lo:lo + 40]
+        want = plain.unit_rms(x.double(), 1e-5) * (1.0 if weight is None else weight.double())
+        out = torch.empty((37, 40), dtype=dtype, device=DEV)
+        ops.slice_rmsnorm(wide.to(DEV)[:, lo:lo + 40], None if weight is None else weight.to(DEV), 1e-5, out)
+        _close(out, want, dtype, f"columns from {lo}")
+
+
 def test_cap_and_added_row(ops):
     g = torch.Generator().manual_seed(1)
     x = torch.randn((7, 131), generator=g) * 20
@@ -134,7 +147,7 @@ def test_router_choice(ops, case):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("geom", [(4, 2, 12, 8, 6, 8, "neox"), (1, 1, 16, 16, 16, 16, "neox"), (6, 3, 10, 24, 0, 16, "neox"),
-                                  (8, 1, 96, 64, 48, 16, "neox"), (2, 2, 8, 6, 4, 8, "interleaved")])
+                                  (8, 1, 80, 64, 40, 16, "neox"), (2, 2, 8, 6, 4, 8, "interleaved")])
 def test_turned_heads_values_and_the_way_back(ops, geom, dtype):
     from tinyinfer_b200.parts.rope import NoPosition, RopeInterleaved, RopeNeox
     heads, kv, dk, dv, rot, ps, kind = geom
@@ -273,11 +286,12 @@ def test_experts_with_identity_among_them(ops, mlp, t, dtype):
 
 MIXER_CASES = [attention(4, 2, 12, 8, 6, 1000.0, 0.29, conv=3), attention(1, 1, 16, 16, 0, 7.0, 0.25, conv=1),
                attention(3, 3, 8, 8, 2, 30.0, 0.35), attention(4, 2, 64, 64, 32, 20000.0, 0.125, conv=4),
-               attention(2, 1, 128, 128, 128, 300000.0, 0.09, conv=2), attention(8, 8, 96, 32, 48, 250.0, 0.1, conv=7),
+               attention(2, 1, 128, 128, 128, 300000.0, 0.09, conv=2), attention(6, 6, 80, 32, 40, 250.0, 0.1, conv=7),
                latent(3, 8, 4, 10, 12, 20, 100.0, 0.3, window=20, scaling=(4.0, 16, 8.0, 1.0)),
                latent(2, 6, 8, 6, 10, 8, 3000.0, 0.35, window=7), latent(1, 16, 2, 16, 8, 8, 30.0, 0.25),
                latent(4, 64, 32, 64, 128, 96, 20000.0, 0.1, window=33, scaling=(16.0, 64, 32.0, 1.0)),
-               latent(2, 128, 64, 128, 64, 64, 1000.0, 0.07, window=16)]
+               latent(2, 128, 64, 128, 64, 64, 1000.0, 0.07, window=16),
+               attention(6, 2, 32, 16, 16, 900.0, 0.18, conv=3), latent(6, 32, 16, 48, 64, 40, 500.0, 0.15, window=50)]
 CUTS = [[("a", 30), ("b", 1)], [("b", 2), ("c", 5)], [("a", 1), ("b", 30), ("c", 1)], [("a", 2), ("c", 1)],
         [("a", 17), ("b", 7), ("c", 33)], [("a", 1)], [("a", 1), ("c", 2)], [("b", 0), ("d", 70)], [("d", 1), ("a", 1)]]
 TOTAL = {"a": 53, "b": 40, "c": 42, "d": 71}

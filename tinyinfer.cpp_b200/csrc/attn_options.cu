@@ -14,6 +14,7 @@
 //    first `v_rot` elements of every value head by frequencies of their own, keys and values go into
 //    the token's page and the queries out.  turn_rows turns the heads of finished rows by plus or minus
 //    their position (the way back for outputs over turned values) and multiplies by sigmoid(gate).
+//  * slice_rmsnorm: the RMS norm (a weight per element) of the first n columns of rows with a stride.
 //  * head_project: out[t, h, :] = in[t, h, :] W[h] with a matrix [n_in, n_out] per head.
 //  * attention_options: one block per (token, query head).  Token i sees key j <= i when j is not
 //    behind the window (i - j < window) and not in an earlier chunk (j >= floor(i / chunk) *
@@ -186,6 +187,20 @@ qk_rownorm_rope_store_kernel(const float* proj, int stride, const float* __restr
         const int j = e % dv, g = e / dv;
         vbase[((size_t)g * page_size + slot) * dv + j] = from_f32<TC>(vrow[e]);
     }
+}
+
+// out[t, :] = x[t, :n] / sqrt(mean(x[t, :n]^2) + eps) * w over rows with a stride: the norm of a column slice of a
+// product (a latent that shares its product with other columns)
+template <typename TO>
+__global__ void __launch_bounds__(256)
+slice_rmsnorm_kernel(const float* x, int stride, int n, const float* __restrict__ w, float eps, TO* __restrict__ out) {
+    __shared__ float scratch[32];
+    const float* row = x + (size_t)blockIdx.x * stride;
+    float ss = 0.0f;
+    for (int e = threadIdx.x; e < n; e += blockDim.x) ss = fmaf(row[e], row[e], ss);
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
+    for (int e = threadIdx.x; e < n; e += blockDim.x)
+        out[(size_t)blockIdx.x * n + e] = from_f32<TO>(row[e] * inv * (w ? w[e] : 1.0f));
 }
 
 template <typename TQ, typename TC>
@@ -553,6 +568,16 @@ extern "C" int ti_qk_rownorm_rope_store(const float* proj, int stride, const flo
     TI_DISPATCH_QC(q_dtype, cache_dtype, CALL)
 #undef CALL
     return ti_check_launch("qk_rownorm_rope_store");
+}
+
+extern "C" int ti_slice_rmsnorm(const float* x, int stride, int num_rows, int n, const float* weight, float eps,
+                                void* out, int out_dtype, void* stream) {
+    if (num_rows == 0 || n == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == TI_BF16) slice_rmsnorm_kernel<bf16><<<num_rows, 256, 0, s>>>(x, stride, n, weight, eps, (bf16*)out);
+    else if (out_dtype == TI_F32) slice_rmsnorm_kernel<float><<<num_rows, 256, 0, s>>>(x, stride, n, weight, eps, (float*)out);
+    else return ti_fail("slice_rmsnorm: output dtype code %d", out_dtype);
+    return ti_check_launch("slice_rmsnorm");
 }
 
 // `qproj` holds a token's query heads of (dk plain | dr rotated), `proj` its latent of `rank` and the key part of dr

@@ -12,6 +12,7 @@ latent_prepare(proj, ...)            normed latent + turned key part as one cach
                                      and turned query parts out
 qkv_turn_store(proj, ...)            no norm: queries and keys turned, values turned by frequencies of
                                      their own, keys/values into pages, queries out
+slice_rmsnorm(x, weight, eps, out)   RMS norm of a column slice of a product
 turn_rows(x, step, rotation, ...)    finished rows' heads turned by plus or minus their position, times
                                      sigmoid(gate)
 head_project(x, w, out)              out[t, h] = x[t, h] @ w[h]
@@ -86,6 +87,7 @@ class MixerOps:
                                             _i, _i, _i, _vp, _vp, _i, _vp, _vp]
             b.ti_qkv_turn_store.argtypes = [_vp, _i, _vp, _i, _i, _f, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i,
                                             _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp]
+            b.ti_slice_rmsnorm.argtypes = [_vp, _i, _i, _i, _vp, _f, _vp, _i, _vp]
             b.ti_turn_rows.argtypes = [_vp, _i, _vp, _vp, _i, _i, _f, _vp, _i, _i, _i, _i, _vp, _vp]
             b.ti_head_project.argtypes = [_vp, _i, _i, _i, _vp, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _vp]
             b.ti_attention_options.argtypes = [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
@@ -180,6 +182,16 @@ class MixerOps:
             bt.data_ptr(), bt.stride(0), pages.data_ptr(), _CODE[pages.dtype], pages.shape[0], cache.page_size,
             t, num_heads, dk, dr, rank, q_plain.data_ptr(), q_full.data_ptr(), _CODE[q_plain.dtype],
             self.status.data_ptr(), self._stream()))
+
+    def slice_rmsnorm(self, x, weight, eps, out):
+        """``out = x / sqrt(mean(x^2) + eps) * weight`` per row, for float32 rows ``x`` that may be a
+        column slice of a wider product (any row stride); ``weight`` float32 per element or None."""
+        t, n = x.shape
+        self._must(x.dtype == torch.float32 and x.stride(1) == 1 and out.is_contiguous() and tuple(out.shape) == (t, n)
+                   and (weight is None or (weight.dtype == torch.float32 and weight.is_contiguous() and weight.shape[0] == n)),
+                   "slice_rmsnorm: float32 rows, a float32 weight per element, contiguous rows out")
+        self._mx(self.mixers.ti_slice_rmsnorm(x.data_ptr(), x.stride(0), t, n, _ptr(weight), float(eps), out.data_ptr(),
+                                              _CODE[out.dtype], self._stream()))
 
     _LAYOUTS = {"interleaved": 0, "neox": 1}
 

@@ -43,7 +43,7 @@ class LatentAttention(Part):
         self.nq = self.num_heads * (self.head_dim + self.rot_dim)
         self.row = self.rank + self.rot_dim
         self.w_in = self.w_o = self.latent_norm = self.sink = self.w_uk = self.w_uv = None
-        self.w_dq = self.w_uq = self.q_norm = None
+        self.w_uq = self.q_norm = None
 
     def weight_specs(self):
         h, nh = self.hidden_size, self.num_heads
@@ -65,9 +65,16 @@ class LatentAttention(Part):
             if q.dtype != dkv.dtype:
                 q, dkv = q.to(torch.float32), dkv.to(torch.float32)
             self.w_in = ops.pack_linear(torch.cat([q, dkv], dim=0))
-        else:
-            self.w_in = ops.pack_linear(tensors["dkv"])
-            self.w_dq, self.w_uq = ops.pack_linear(tensors["dq"]), ops.pack_linear(tensors["uq"])
+        else:                                         # the two latents as one product: [query latent | latent | key part]
+            dq, dkv = tensors["dq"], tensors["dkv"]
+            if dq.dtype != dkv.dtype:
+                dq, dkv = dq.to(torch.float32), dkv.to(torch.float32)
+            mats = [dq, dkv]
+            rows = dq.shape[0] + dkv.shape[0]
+            if rows % 16:                             # zero rows up to a width the tensor-core products take
+                mats.append(torch.zeros((16 - rows % 16, self.hidden_size), dtype=dq.dtype, device=dq.device))
+            self.w_in = ops.pack_linear(torch.cat(mats, dim=0))
+            self.w_uq = ops.pack_linear(tensors["uq"])
             self.q_norm = as_float32(tensors["dq.norm"]).contiguous()
         self.w_o = ops.pack_linear(tensors["o"])
         self.latent_norm = as_float32(tensors["dkv.norm"]).contiguous()
@@ -89,12 +96,11 @@ class LatentAttention(Part):
         ops.linear(h, self.w_in, proj)
         q_proj = None
         if self.q_rank is not None:                   # the queries through their own normed latent
-            q_lat = torch.empty((t, self.q_rank), dtype=torch.float32, device=h.device)
-            ops.linear(h, self.w_dq, q_lat)
-            q_lat_n = torch.empty((t, self.q_rank), dtype=h.dtype, device=h.device)
-            ops.rmsnorm(q_lat, self.q_norm, self.eps, q_lat_n)
+            q_lat = torch.empty((t, self.q_rank), dtype=h.dtype, device=h.device)
+            ops.slice_rmsnorm(proj[:, :self.q_rank], self.q_norm, self.eps, q_lat)
             q_proj = torch.empty((t, self.nq), dtype=torch.float32, device=h.device)
-            ops.linear(q_lat_n, self.w_uq, q_proj)
+            ops.linear(q_lat, self.w_uq, q_proj)
+            proj = proj[:, self.q_rank:]
         q_plain = torch.empty((t, nh * self.head_dim), dtype=h.dtype, device=h.device)
         q_full = torch.empty((t, nh, self.row), dtype=h.dtype, device=h.device)
         ops.latent_prepare(proj, self.latent_norm, self.eps, self.position.rotation(h.device), step, cache,
