@@ -43,20 +43,23 @@ __device__ __forceinline__ float turned(const float* x, int j, float pos, const 
     return (j & 1) ? a * c + b * s : a * c - b * s;
 }
 
-// element j of a head x whose first `rot` elements are turned by `pos`: neighbours (2i, 2i + 1) form pair
-// i, or, `halves`, elements (i, i + rot/2); both the sine and the cosine are multiplied by `mag`
-__device__ __forceinline__ float turned_at(const float* x, int j, int rot, int halves, float pos,
-                                           const float* __restrict__ inv_freq, float mag) {
-    if (j >= rot) return x[j];
+// The turn of a head by a table of the token's cosines and sines (`cs[pair]`, made once per token: the angle
+// depends on the position and the pair alone, not on the head).  A head of n elements whose first `rot` are
+// turned has rot/2 pairs and n - rot single elements: item i < rot/2 is pair i, the others are singles.
+struct TurnItem { int a, b; };      // the pair's two elements (b < 0: a single element a)
+__device__ __forceinline__ TurnItem turn_item(int i, int rot, int halves) {
     const int half = rot >> 1;
-    const int pair = halves ? (j < half ? j : j - half) : (j >> 1);
-    const bool second = halves ? j >= half : (j & 1);
-    const int other = halves ? (second ? j - half : j + half) : (j ^ 1);
-    float s, c;
-    sincosf(pos * inv_freq[pair], &s, &c);
-    s *= mag;
-    c *= mag;
-    return second ? x[j] * c + x[other] * s : x[j] * c - x[other] * s;
+    if (i >= half) return {rot + (i - half), -1};
+    return halves ? TurnItem{i, i + half} : TurnItem{2 * i, 2 * i + 1};
+}
+
+__device__ __forceinline__ void fill_turn_table(float2* cs, int pairs, float pos, const float* __restrict__ inv_freq,
+                                                float mag) {
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        float s, c;
+        sincosf(pos * inv_freq[i], &s, &c);
+        cs[i] = make_float2(c * mag, s * mag);
+    }
 }
 
 template <typename TQ, typename TC>
@@ -67,14 +70,27 @@ qkv_turn_store_kernel(const float* proj, int stride, const float* __restrict__ i
                       const int* __restrict__ block_table, int bt_stride, TC* __restrict__ pages, int num_pages,
                       int page_size, int write_kv, int num_heads, int num_kv_heads, int dk, int dv,
                       TQ* __restrict__ q_out, int* __restrict__ status) {
+    extern __shared__ float2 turn_table[];             // rot/2 entries for queries and keys, then v_rot/2 for values
     const int t = blockIdx.x;
-    const int nq = num_heads * dk, nk = num_kv_heads * dk, nv = num_kv_heads * dv;
+    const int nq = num_heads * dk, nk = num_kv_heads * dk;
     const float* row = proj + (size_t)t * stride;
     const int pos_i = positions[t];
     const float pos = (float)pos_i;
-    for (int e = threadIdx.x; e < nq; e += blockDim.x) {
-        const int j = e % dk;
-        q_out[(size_t)t * nq + e] = from_f32<TQ>(turned_at(row + (e - j), j, rot, halves, pos, inv_freq, mag));
+    float2* cs = turn_table;
+    float2* vcs = turn_table + (rot >> 1);
+    fill_turn_table(cs, rot >> 1, pos, inv_freq, mag);
+    if (write_kv) fill_turn_table(vcs, v_rot >> 1, pos, v_inv_freq, 1.0f);
+    __syncthreads();
+    const int per_head = (rot >> 1) + (dk - rot);      // items of a query or key head
+    for (int e = threadIdx.x; e < num_heads * per_head; e += blockDim.x) {
+        const int h = e / per_head, i = e % per_head;
+        const TurnItem it = turn_item(i, rot, halves);
+        const float* x = row + (size_t)h * dk;
+        TQ* dst = q_out + (size_t)t * nq + (size_t)h * dk;
+        if (it.b < 0) { dst[it.a] = from_f32<TQ>(x[it.a]); continue; }
+        const float2 f = cs[i];
+        dst[it.a] = from_f32<TQ>(x[it.a] * f.x - x[it.b] * f.y);
+        dst[it.b] = from_f32<TQ>(x[it.b] * f.x + x[it.a] * f.y);
     }
     if (!write_kv) return;
     const int page = block_table[(size_t)req_of_tok[t] * bt_stride + pos_i / page_size];
@@ -85,36 +101,61 @@ qkv_turn_store_kernel(const float* proj, int stride, const float* __restrict__ i
     const int slot = pos_i % page_size;
     TC* base = pages + (size_t)page * num_kv_heads * page_size * (dk + dv);
     const float* krow = row + nq;
-    for (int e = threadIdx.x; e < nk; e += blockDim.x) {
-        const int j = e % dk, g = e / dk;
-        base[((size_t)g * page_size + slot) * dk + j] =
-            from_f32<TC>(turned_at(krow + (e - j), j, rot, halves, pos, inv_freq, mag));
+    for (int e = threadIdx.x; e < num_kv_heads * per_head; e += blockDim.x) {
+        const int g = e / per_head, i = e % per_head;
+        const TurnItem it = turn_item(i, rot, halves);
+        const float* x = krow + (size_t)g * dk;
+        TC* dst = base + ((size_t)g * page_size + slot) * dk;
+        if (it.b < 0) { dst[it.a] = from_f32<TC>(x[it.a]); continue; }
+        const float2 f = cs[i];
+        dst[it.a] = from_f32<TC>(x[it.a] * f.x - x[it.b] * f.y);
+        dst[it.b] = from_f32<TC>(x[it.b] * f.x + x[it.a] * f.y);
     }
     TC* vbase = base + (size_t)num_kv_heads * page_size * dk;
     const float* vrow = krow + nk;
-    for (int e = threadIdx.x; e < nv; e += blockDim.x) {
-        const int j = e % dv, g = e / dv;
-        vbase[((size_t)g * page_size + slot) * dv + j] =
-            from_f32<TC>(turned_at(vrow + (e - j), j, v_rot, v_halves, pos, v_inv_freq, 1.0f));
+    const int v_per_head = (v_rot >> 1) + (dv - v_rot);
+    for (int e = threadIdx.x; e < num_kv_heads * v_per_head; e += blockDim.x) {
+        const int g = e / v_per_head, i = e % v_per_head;
+        const TurnItem it = turn_item(i, v_rot, v_halves);
+        const float* x = vrow + (size_t)g * dv;
+        TC* dst = vbase + ((size_t)g * page_size + slot) * dv;
+        if (it.b < 0) { dst[it.a] = from_f32<TC>(x[it.a]); continue; }
+        const float2 f = vcs[i];
+        dst[it.a] = from_f32<TC>(x[it.a] * f.x - x[it.b] * f.y);
+        dst[it.b] = from_f32<TC>(x[it.b] * f.x + x[it.a] * f.y);
     }
 }
 
-// x[t, h, :] turned by sign * position over its first `rot` elements, then times sigmoid(gate[t, h * n + j]);
-// a block per (token, head), so the rows may be turned in place
+// x[t, h, :] turned by sign * position over its first `rot` elements, then times sigmoid(gate[t, h * n + j]); a
+// block per token, a thread reads and writes both elements of a pair, so the rows may be turned in place
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 turn_rows_kernel(const T* x, const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot,
                  int halves, float sign, const float* gate, int gate_stride, int num_heads, int n, T* out) {
-    extern __shared__ float head_row[];                // the head in float32
-    const int t = blockIdx.x, h = blockIdx.y;
-    const size_t at = ((size_t)t * num_heads + h) * n;
-    for (int j = threadIdx.x; j < n; j += blockDim.x) head_row[j] = to_f32(x[at + j]);
+    extern __shared__ float2 turn_table[];
+    const int t = blockIdx.x;
+    fill_turn_table(turn_table, rot >> 1, sign * (float)positions[t], inv_freq, 1.0f);
     __syncthreads();
-    const float pos = sign * (float)positions[t];
-    for (int j = threadIdx.x; j < n; j += blockDim.x) {
-        float y = turned_at(head_row, j, rot, halves, pos, inv_freq, 1.0f);
-        if (gate) y *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + (size_t)h * n + j]));
-        out[at + j] = from_f32<T>(y);
+    const int per_head = (rot >> 1) + (n - rot);
+    const float* gt = gate ? gate + (size_t)t * gate_stride : nullptr;
+    for (int e = threadIdx.x; e < num_heads * per_head; e += blockDim.x) {
+        const int h = e / per_head, i = e % per_head;
+        const TurnItem it = turn_item(i, rot, halves);
+        const size_t at = ((size_t)t * num_heads + h) * n;
+        const float a = to_f32(x[at + it.a]);
+        if (it.b < 0) {
+            out[at + it.a] = from_f32<T>(gt ? a / (1.0f + expf(-gt[(size_t)h * n + it.a])) : a);
+            continue;
+        }
+        const float b = to_f32(x[at + it.b]);
+        const float2 f = turn_table[i];
+        float ya = a * f.x - b * f.y, yb = b * f.x + a * f.y;
+        if (gt) {
+            ya *= 1.0f / (1.0f + expf(-gt[(size_t)h * n + it.a]));
+            yb *= 1.0f / (1.0f + expf(-gt[(size_t)h * n + it.b]));
+        }
+        out[at + it.a] = from_f32<T>(ya);
+        out[at + it.b] = from_f32<T>(yb);
     }
 }
 
@@ -615,8 +656,10 @@ extern "C" int ti_qkv_turn_store(const float* proj, int stride, const float* inv
     TI_REQUIRE((rot == 0 || inv_freq != nullptr) && (v_rot == 0 || v_inv_freq != nullptr),
                "qkv_turn_store: a rotation needs its frequencies");
     cudaStream_t s = (cudaStream_t)stream;
+    const size_t turn_smem = (size_t)(rot / 2 + v_rot / 2) * sizeof(float2);      // the token's cosines and sines
+    TI_REQUIRE(turn_smem <= 48 * 1024, "qkv_turn_store: rotated widths %d and %d", rot, v_rot);
 #define CALL(TQ, TC)                                                                              \
-    qkv_turn_store_kernel<TQ, TC><<<num_tokens, 256, 0, s>>>(                                      \
+    qkv_turn_store_kernel<TQ, TC><<<num_tokens, 256, turn_smem, s>>>(                              \
         proj, stride, inv_freq, rot, halves, mag, v_inv_freq, v_rot, v_halves, positions, req_of_tok, \
         block_table, bt_stride, (TC*)pages, num_pages, page_size, write_kv, num_heads, num_kv_heads, dk, dv, \
         (TQ*)q_out, status)
@@ -631,16 +674,15 @@ extern "C" int ti_turn_rows(const void* x, int dtype, const int* positions, cons
     if (num_tokens == 0 || num_heads == 0) return 0;
     TI_REQUIRE(rot >= 0 && rot <= n && rot % 2 == 0, "turn_rows: rotated width %d must be even and at most %d", rot, n);
     TI_REQUIRE(rot == 0 || inv_freq != nullptr, "turn_rows: a rotation needs its frequencies");
-    const size_t smem = (size_t)n * sizeof(float);
-    TI_REQUIRE(n <= 8192 && num_heads <= 65535, "turn_rows: %d heads of %d elements", num_heads, n);
+    const size_t smem = (size_t)(rot / 2) * sizeof(float2);
+    TI_REQUIRE(smem <= 48 * 1024, "turn_rows: a rotated width of %d", rot);
     cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid(num_tokens, num_heads);
     if (dtype == TI_BF16)
-        turn_rows_kernel<bf16><<<grid, 128, smem, s>>>((const bf16*)x, positions, inv_freq, rot, halves, sign, gate,
-                                                      gate_stride, num_heads, n, (bf16*)out);
+        turn_rows_kernel<bf16><<<num_tokens, 256, smem, s>>>((const bf16*)x, positions, inv_freq, rot, halves, sign, gate,
+                                                            gate_stride, num_heads, n, (bf16*)out);
     else if (dtype == TI_F32)
-        turn_rows_kernel<float><<<grid, 128, smem, s>>>((const float*)x, positions, inv_freq, rot, halves, sign,
-                                                       gate, gate_stride, num_heads, n, (float*)out);
+        turn_rows_kernel<float><<<num_tokens, 256, smem, s>>>((const float*)x, positions, inv_freq, rot, halves, sign,
+                                                             gate, gate_stride, num_heads, n, (float*)out);
     else return ti_fail("turn_rows: dtype code %d", dtype);
     return ti_check_launch("turn_rows");
 }
