@@ -159,3 +159,60 @@ def make_model(tmp_path, name: str, seed: int = 11) -> str:
             json.dump(SMALL[name], fh)
         write_safetensors(os.path.join(d, "model.safetensors"), random_weights(SMALL[name], seed))
     return d
+
+
+def drawn_configuration(seed: int) -> dict:
+    """A configuration whose every size, constant, option and order of layers is drawn from ``seed``."""
+    import random
+    r = random.Random(seed)
+    pick = r.choice
+    width = pick([16, 24, 40, 64, 72])
+
+    def drawn_moe():
+        if r.random() < 0.15:
+            return None
+        experts, identity = pick([1, 2, 3, 5, 8]), pick([0, 0, 1, 2, 3])
+        total = experts + identity
+        counts = [c for c in (1, 2, 3, 4) if total % c == 0]
+        count = pick(counts)
+        keep = r.randint(1, count)
+        top = r.randint(1, min(total // count * keep, 4))
+        groups = (count, keep) if (count > 1 or r.random() < 0.3) else None
+        return moe(experts, top, pick([8, 16, 24, 32]), pick([0.5, 1.0, 3.0]), identity=identity if identity or r.random() < 0.5 else None,
+                   groups=groups)
+
+    layers = []
+    for _ in range(r.randint(1, 5)):
+        if r.random() < 0.5:
+            kv = pick([1, 2, 3])
+            heads = kv * pick([1, 2, 3])
+            dim, vdim = pick([4, 6, 10, 16, 32, 48]), pick([2, 6, 8, 16, 32, 40])
+            rot = pick([0, 2, dim // 2 // 2 * 2, dim])
+            entry = attention(heads, kv, dim, vdim, rot, pick([10.0, 500.0, 250000.0]), r.uniform(0.05, 0.4),
+                              conv=pick([None, 1, 2, 3, 4, 6]))
+        else:
+            rot_dim = pick([2, 4, 8, 16])
+            scaling = None if r.random() < 0.4 else (pick([2.0, 8.0, 40.0]), pick([8, 32, 256]), pick([32.0, 4.0]), pick([1.0, 2.0]))
+            entry = latent(pick([1, 2, 3, 4, 5]), pick([4, 8, 16, 24]), rot_dim, pick([4, 8, 12, 16]), pick([6, 16, 32, 48]),
+                           pick([4, 16, 40]), pick([50.0, 10000.0]), r.uniform(0.05, 0.4),
+                           window=pick([None, 1, 2, 5, 16, 17, 33, 64, 200]), scaling=scaling)
+        layers.append(layer(entry, drawn_moe()))
+    cfg = {"architecture": "Nekorax", "vocab": pick([33, 100, 257]), "width": width, "embedding": {"scale": r.uniform(0.3, 2.0)},
+           "norm": {"eps": pick([1e-6, 1e-5])}, "layers": layers}
+    if r.random() < 0.8:
+        cfg["logit_softcap"] = pick([5.0, 15.0, 50.0])
+    if r.random() < 0.8:
+        start = r.randint(0, len(layers) - 1)
+        cfg["loop"] = {"start": start, "stop": r.randint(start + 1, len(layers)), "times": pick([1, 2, 2, 3])}
+    return cfg
+
+
+def make_drawn_model(tmp_path, seed: int) -> str:
+    d = os.path.join(str(tmp_path), f"nekorax_drawn_{seed}")
+    if not os.path.isdir(d):
+        os.makedirs(d)
+        cfg = drawn_configuration(seed)
+        with open(os.path.join(d, "config.json"), "w") as fh:
+            json.dump(cfg, fh)
+        write_safetensors(os.path.join(d, "model.safetensors"), random_weights(cfg, seed))
+    return d

@@ -385,6 +385,21 @@ def test_cuttings_agree_with_the_plain_implementation(tmp_path_factory, name, fa
     _compare(steps, out, _plain(d, name), dtype, f"{name} {family}")
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_drawn_configurations(tmp_path_factory, seed):
+    """Sizes, constants, options and the order of layers drawn from a seed: mixed batches in a small pool in
+    float32, whole prompts in bfloat16."""
+    from nekorax_util import make_drawn_model
+    d = make_drawn_model(tmp_path_factory.getbasetemp(), seed)
+    cfg, w = plain.load_folder(d)
+    reqs = {f"r{i}": random_tokens(cfg["vocab"], n, seed=seed * 10 + i) for i, n in enumerate([70, 45, 33, 2, 97, 1])}
+    want = {r: plain.forward(cfg, w, t) for r, t in reqs.items()}
+    steps = traces.mixed(reqs, seed=seed)
+    _compare(steps, _run(d, "float32", steps, traces.max_live_tokens(steps)), want, "float32", f"drawn {seed} mixed")
+    steps = traces.whole(reqs)
+    _compare(steps, _run(d, "bfloat16", steps, traces.max_live_tokens(steps)), want, "bfloat16", f"drawn {seed} whole")
+
+
 def test_one_state_slot_used_by_every_request_in_turn(tmp_path_factory):
     d = make_model(tmp_path_factory.getbasetemp(), "A")
     steps = traces.portions(_requests("A"), sizes=(40, 2, 9))
